@@ -1,5 +1,5 @@
 from .pools import IdPool, PoolError
-from .manager import CacheManager, OutOfPages, OutOfSlots, PagedKVView, RequestCache, SlotView
+from .manager import CacheManager, OutOfPages, OutOfSlots, PagedKVView, PagedRowsView, RequestCache, SlotView
 
-__all__ = ["IdPool", "PoolError", "CacheManager", "OutOfPages", "OutOfSlots", "PagedKVView", "RequestCache",
+__all__ = ["IdPool", "PoolError", "CacheManager", "OutOfPages", "OutOfSlots", "PagedKVView", "PagedRowsView", "RequestCache",
            "SlotView"]

@@ -7,7 +7,9 @@ Two kinds of memory, both sized once at start:
   last ``window`` keys).  A group has a pool of page ids of its own and every
   request has one block table per group; a page id addresses the same page in
   the key and value tensors of every entry of the group
-  (``[n_pages, kv_heads, page_size, head_dim]`` each).  Pages are taken as a
+  (``[n_pages, kv_heads, page_size, head_dim]`` each), and in the row tensors
+  (``[n_pages, page_size, width]``) of entries that keep one plain row per
+  position (``PagedRows``).  Pages are taken as a
   request grows, given back when it ends, and in a windowed group also as
   soon as the window has passed them; the ids are then reused by whoever asks
   next.
@@ -26,7 +28,7 @@ from typing import Optional
 
 import torch
 
-from ..parts.base import PagedKV, SlotState
+from ..parts.base import PagedKV, PagedRows, SlotState
 from .pools import IdPool, PoolError
 
 
@@ -43,6 +45,16 @@ class PagedKVView:
     """What a mixer sees of its paged cache during one step."""
     k_pages: torch.Tensor
     v_pages: torch.Tensor
+    block_table: torch.Tensor          # int32 [requests in the step, max_blocks]
+    page_size: int
+    writable: bool
+    window: Optional[int]
+
+
+@dataclass
+class PagedRowsView:
+    """What a mixer sees of its pages of plain rows during one step."""
+    pages: torch.Tensor                # [n_pages, page_size, width]
     block_table: torch.Tensor          # int32 [requests in the step, max_blocks]
     page_size: int
     writable: bool
@@ -103,7 +115,7 @@ class CacheManager:
             if reads is not None:
                 continue
             for k, need in enumerate(needs):
-                if isinstance(need, PagedKV):
+                if isinstance(need, (PagedKV, PagedRows)):
                     if need.window not in by_window:
                         count = n_pages[need.window] if isinstance(n_pages, dict) else n_pages
                         by_window[need.window] = len(self.groups)
@@ -111,6 +123,10 @@ class CacheManager:
                     g = by_window[need.window]
                     self.groups[g].entries.append((e, k))
                     self._group_of[(e, k)] = g
+                    if isinstance(need, PagedRows):
+                        self._pages[(e, k)] = (self._page_tensor((self.groups[g].pool.size, page_size, need.width),
+                                                                 dtype), None)
+                        continue
                     shape = (self.groups[g].pool.size, need.kv_heads, page_size)
                     self._pages[(e, k)] = (self._page_tensor(shape + (need.head_dim,), dtype),
                                            self._page_tensor(shape + (need.value_dim,), dtype))
@@ -161,7 +177,10 @@ class CacheManager:
     def kv_bytes_per_token(self) -> int:
         total = 0
         for (e, k), (kp, vp) in self._pages.items():
-            total += kp.shape[1] * (kp.shape[3] + vp.shape[3]) * kp.element_size()
+            if vp is None:
+                total += kp.shape[2] * kp.element_size()
+            else:
+                total += kp.shape[1] * (kp.shape[3] + vp.shape[3]) * kp.element_size()
         return total
 
     def pages_needed(self, length: int) -> int:
@@ -311,7 +330,11 @@ class CacheManager:
             owner = e if reads is None else reads
             views = []
             for k, need in enumerate(self.entry_needs[owner][0]):
-                if isinstance(need, PagedKV):
+                if isinstance(need, PagedRows):
+                    g = self._group_of[(owner, k)]
+                    views.append(PagedRowsView(self._pages[(owner, k)][0], block_tables[g], self.page_size,
+                                               reads is None, need.window))
+                elif isinstance(need, PagedKV):
                     kp, vp = self._pages[(owner, k)]
                     g = self._group_of[(owner, k)]
                     views.append(PagedKVView(kp, vp, block_tables[g], self.page_size, reads is None, need.window))

@@ -1,8 +1,10 @@
 from .plan import ModelPlan, LayerSpec, OrderEntry, PartSpec, prenorm_layer
 from .registry import register_architecture, known_architectures, detect, parse_config
 from .lfm2 import Lfm2Config, ConfigError
+from .potivik import PotivikConfig
 
 register_architecture("Lfm2ForCausalLM", Lfm2Config.from_dict, model_types=("lfm2",))
+register_architecture("Potivik", PotivikConfig.from_dict, model_types=("potivik",))
 
 __all__ = ["ModelPlan", "LayerSpec", "OrderEntry", "PartSpec", "prenorm_layer", "register_architecture", "known_architectures",
-           "detect", "parse_config", "Lfm2Config", "ConfigError"]
+           "detect", "parse_config", "Lfm2Config", "PotivikConfig", "ConfigError"]

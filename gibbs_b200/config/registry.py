@@ -32,8 +32,8 @@ def known_architectures() -> list[str]:
 
 
 def detect(cfg: dict, forced: Optional[str] = None) -> Architecture:
-    """The architecture a config.json names: by ``architectures`` first, then
-    by ``model_type``; ``forced`` skips detection (the reference's ``--arch``,
+    """The architecture a config.json names: by ``architectures`` (or the single
+    string ``architecture``) first, then by ``model_type``; ``forced`` skips detection (the reference's ``--arch``,
     ``src/main.rs:180-183``)."""
     if forced is not None:
         if forced in _ARCHITECTURES:
@@ -42,7 +42,8 @@ def detect(cfg: dict, forced: Optional[str] = None) -> Architecture:
             if forced in a.model_types:
                 return a
         raise KeyError(f"unknown architecture '{forced}'; known: {known_architectures()}")
-    for name in cfg.get("architectures") or []:
+    one = cfg.get("architecture")            # some designs name themselves with one string
+    for name in list(cfg.get("architectures") or []) + ([one] if isinstance(one, str) else []):
         if name in _ARCHITECTURES:
             return _ARCHITECTURES[name]
     mt = cfg.get("model_type")
@@ -50,7 +51,7 @@ def detect(cfg: dict, forced: Optional[str] = None) -> Architecture:
         if mt is not None and mt in a.model_types:
             return a
     raise KeyError(
-        f"config.json names architectures {cfg.get('architectures')} / model_type {mt!r}; "
+        f"config.json names architectures {cfg.get('architectures') or cfg.get('architecture')} / model_type {mt!r}; "
         f"known: {known_architectures()}")
 
 

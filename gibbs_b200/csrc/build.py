@@ -24,11 +24,14 @@ HERE = Path(__file__).resolve().parent
 
 # library name -> sources.  A model needs "core" always and "tensorcore" when
 # it computes in bfloat16; "runtime" holds no kernels: it walks a step's list of operations
-# and calls into the other two.
+# and calls into the others; "hybrid" is built when a model has a part that launches from it.
 LIBRARIES = {
     "core": ["errors.cu", "elementwise.cu", "gemm_simt.cu", "conv.cu", "attention.cu", "sampling.cu"],
     "tensorcore": ["errors.cu", "gemm_tc.cu", "gemm_tc_decode.cu", "attention_tc.cu", "attention_tcgen05.cu"],
     "runtime": ["errors.cu", "step_plan.cu"],
+    # layer norms, clamped gated units, latent attention, state-space recurrences, routed experts: every entry
+    # point has the signature of a step-plan operation (hybrid.cuh)
+    "hybrid": ["errors.cu", "norms.cu", "latent_attention.cu", "ssm.cu", "moe.cu"],
 }
 
 NVCC_FLAGS = [

@@ -1,0 +1,255 @@
+// Attention over a compressed ("latent") key/value cache, in the absorbed form.
+//
+// A token's cache row is [c | k_rot]: the RMS-normed latent c (kv_rank values), from which every head's
+// unrotated keys W_uk c and values W_uv c derive, and one rotated key part shared by all heads.  With
+//   q'_h = [W_uk,h^T q_plain,h | rot(q_rot,h)]
+// the score of head h against a cached row is q'_h . [c | k_rot], and the head's output is
+// W_uv,h (sum_j p_j c_j): nothing but the cache rows is read per key, for prompts and decoding alike.
+//
+//  gb_op_latent_prep       RMS norm of the latent and rotation of the shared key part, written into the
+//                          token's page; rotation of the queries' rotated parts into q'
+//  gb_op_head_linear       out[t, h, :] = x[t, h, :] W[h]^T for every head (absorbing W_uk, applying W_uv)
+//  gb_op_latent_attention  softmax(scale * q' . rows) over the last `window` rows (all when 0), times the
+//                          rows' latent part, times sigmoid(gate[t, h]); scores and weights in 32-bit
+//
+// Rotation: the first `rot_dims` entries of a rotated part turn in adjacent pairs (2i, 2i+1) by
+// pos * inv_freq[i] (angle in 32-bit); the rest passes unchanged.
+// Pages: [n_pages, page_size, kv_rank + rot_dim]; a page id outside the pool is never dereferenced: the
+// access is skipped and *status is set.
+#include "hybrid.cuh"
+
+namespace {
+
+enum { STATUS_BAD_PAGE_WRITE = 1, STATUS_BAD_PAGE_READ = 2 };
+
+// one block per token: warp 0 writes the cache row, the others rotate the heads' queries
+template <typename TC>
+__global__ void latent_prep_kernel(const float* fused, long long ld, int dkv_col, const float* __restrict__ gain,
+                                   const float* __restrict__ inv_freq, int rot_dims, const int* tok_req,
+                                   const int* tok_pos, const int* block_table, int bt_stride, int page_size, TC* pages,
+                                   int n_pages, int H, int dn, int dr, int r, float* qp, float eps, int* status) {
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int pos = tok_pos[t];
+  const int half = rot_dims >> 1;
+  pdl_wait();
+  const float* row = fused + (size_t)t * ld;
+  if (warp == 0) {
+    const int page = block_table[(size_t)tok_req[t] * bt_stride + pos / page_size];
+    if (page < 0 || page >= n_pages) {
+      if (lane == 0) atomicExch(status, STATUS_BAD_PAGE_WRITE);
+    } else {
+      TC* dst = pages + ((size_t)page * page_size + pos % page_size) * (r + dr);
+      const float* lat = row + dkv_col;
+      float ss = 0.f;
+      for (int d = lane; d < r; d += 32) ss += lat[d] * lat[d];
+      const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)r + eps);
+      for (int d = lane; d < r; d += 32) dst[d] = from_f32<TC>(lat[d] * rstd * gain[d]);
+      const float* kr = lat + r;
+      for (int j = lane; j < half; j += 32) {
+        const float ang = (float)pos * inv_freq[j];
+        const float c = cosf(ang), s = sinf(ang);
+        const float u = kr[2 * j], v = kr[2 * j + 1];
+        dst[r + 2 * j] = from_f32<TC>(u * c - v * s);
+        dst[r + 2 * j + 1] = from_f32<TC>(v * c + u * s);
+      }
+      for (int d = 2 * half + lane; d < dr; d += 32) dst[r + d] = from_f32<TC>(kr[d]);
+    }
+  }
+  const int w0 = warps > 1 ? 1 : 0, step = warps > 1 ? warps - 1 : 1;
+  if (warps > 1 && warp == 0) return;
+  for (int h = warp - w0; h < H; h += step) {
+    const float* q = row + (size_t)h * (dn + dr) + dn;
+    float* o = qp + ((size_t)t * H + h) * (r + dr) + r;
+    for (int j = lane; j < half; j += 32) {
+      const float ang = (float)pos * inv_freq[j];
+      const float c = cosf(ang), s = sinf(ang);
+      const float u = q[2 * j], v = q[2 * j + 1];
+      o[2 * j] = u * c - v * s;
+      o[2 * j + 1] = v * c + u * s;
+    }
+    for (int d = 2 * half + lane; d < dr; d += 32) o[d] = q[d];
+  }
+}
+
+template <typename TW, typename TO>
+__global__ void head_linear_kernel(const float* x, long long ldx, long long xh, const TW* __restrict__ W, TO* out,
+                                   long long ldo, long long oh, int n, int O, int I) {
+  pdl_trigger();
+  pdl_wait();
+  const int h = blockIdx.z, r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+  const float* xb = x + (size_t)h * xh;
+  const TW* wb = W + (size_t)h * O * I;
+  float acc[4][4];
+  int ty, tx;
+  hy_tile_64x64<float, TW>(
+      [&](int i) -> const float* { return r0 + i < n ? xb + (size_t)(r0 + i) * ldx : nullptr; },
+      [&](int j) -> const TW* { return c0 + j < O ? wb + (size_t)(c0 + j) * I : nullptr; }, I, acc, ty, tx);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int row = r0 + ty * 4 + r;
+    if (row >= n) continue;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int col = c0 + tx * 4 + c;
+      if (col < O) out[(size_t)row * ldo + (size_t)h * oh + col] = from_f32<TO>(acc[r][c]);
+    }
+  }
+}
+
+// One block per (token, group of up to HB heads); one warp per head.  Key rows arrive in tiles of 32
+// in shared memory (32-bit), shared by the block's heads.  Lane j scores key j of the tile; the output's
+// columns are spread over the lanes (RL per lane).
+constexpr int LA_HB = 8, LA_KT = 32;
+
+template <typename TC, int RL>
+__global__ void latent_attention_kernel(const float* qp, const TC* pages, const int* block_table, int bt_stride,
+                                        int page_size, int n_pages, const int* tok_req, const int* tok_pos,
+                                        const float* gate, long long ld_gate, float* out, long long ldo, int H, int r,
+                                        int dr, float scale, int window, int* status) {
+  extern __shared__ __align__(16) float smem[];
+  pdl_trigger();
+  const int Dk = r + dr, Dp = Dk + 1;
+  float* qs = smem;                        // [LA_HB][Dk]
+  float* ks = smem + LA_HB * Dk;           // [LA_KT][Dp]
+  const int t = blockIdx.x, h0 = blockIdx.y * LA_HB;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int h = h0 + warp;
+  const bool live = h < H;
+  const int pos = tok_pos[t];
+  const int* table = block_table + (size_t)tok_req[t] * bt_stride;
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  pdl_wait();
+  for (int i = threadIdx.x; i < LA_HB * Dk; i += blockDim.x) {
+    const int hh = h0 + i / Dk;
+    qs[i] = hh < H ? qp[((size_t)t * H + hh) * Dk + (i % Dk)] : 0.f;
+  }
+  float m = -INFINITY, l = 0.f, acc[RL];
+#pragma unroll
+  for (int i = 0; i < RL; ++i) acc[i] = 0.f;
+  const float* q = qs + warp * Dk;
+  for (int k0 = lo; k0 <= pos; k0 += LA_KT) {
+    __syncthreads();                       // the last tile has been used (and q is in place)
+    for (int i = threadIdx.x; i < LA_KT * Dk; i += blockDim.x) {
+      const int j = i / Dk, d = i - j * Dk;
+      const int kp = k0 + j;
+      float v = 0.f;
+      if (kp <= pos) {
+        const int page = table[kp / page_size];
+        if (page < 0 || page >= n_pages) {
+          if (d == 0) atomicExch(status, STATUS_BAD_PAGE_READ);
+        } else {
+          v = to_f32(pages[((size_t)page * page_size + kp % page_size) * Dk + d]);
+        }
+      }
+      ks[j * Dp + d] = v;
+    }
+    __syncthreads();
+    if (!live) continue;
+    float s = -INFINITY;
+    if (k0 + lane <= pos) {
+      const float* kr = ks + lane * Dp;
+      float dot = 0.f;
+      for (int d = 0; d < Dk; ++d) dot = fmaf(q[d], kr[d], dot);
+      s = dot * scale;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float corr = expf(m - m_new);    // (0 on the first tile: m = -inf)
+    const float p = k0 + lane <= pos ? expf(s - m_new) : 0.f;
+    l = l * corr + warp_sum(p);
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < RL; ++i) acc[i] *= corr;
+    const int n_keys = min(LA_KT, pos - k0 + 1);
+    for (int j = 0; j < n_keys; ++j) {
+      const float pj = __shfl_sync(0xffffffffu, p, j);
+      const float* kr = ks + j * Dp;
+#pragma unroll
+      for (int i = 0; i < RL; ++i) {
+        const int d = lane + 32 * i;
+        if (d < r) acc[i] = fmaf(pj, kr[d], acc[i]);
+      }
+    }
+  }
+  if (!live) return;
+  const float g = gate ? hy_sigmoid(gate[(size_t)t * ld_gate + h]) : 1.f;
+  const float inv = g / l;
+  float* o = out + (size_t)t * ldo + (size_t)h * r;
+#pragma unroll
+  for (int i = 0; i < RL; ++i) {
+    const int d = lane + 32 * i;
+    if (d < r) o[d] = acc[i] * inv;
+  }
+}
+
+}  // namespace
+
+// a0 fused rows [q heads (plain | rotated) | ... ] (f32), a1 their stride, a2 column of [latent | rotated key],
+// a3 gain of the latent's norm [r], a4 inv_freq [rot_dims / 2], a5 rot_dims, a6 token -> request, a7 token ->
+// position, a8 block table, a9 its entries per request, a10 page size, a11 pages, a12 number of pages, a13 their dtype,
+// a14 tokens, a15 heads, a16 plain query size, a17 rotated size, a18 latent size, a19 q' [tokens, heads, r + rot]
+// (f32); f0 eps
+GB_OP(gb_op_latent_prep) {
+  const int n = (int)a[14], H = (int)a[15];
+  if (n <= 0) return 0;
+  if (a[5] % 2 || a[5] > a[17]) GB_FAIL(GB_ERR_ARG, "latent_prep: %lld rotated dimensions of %lld", a[5], a[17]);
+  const int warps = H + 1 < 8 ? H + 1 : 8;
+#define PREP(TC)                                                                                                       \
+  gb_launch(latent_prep_kernel<TC>, dim3(n), dim3(32 * warps), 0, ctx->stream, op_ptr<const float>(a[0]), a[1], (int)a[2], \
+            op_ptr<const float>(a[3]), op_ptr<const float>(a[4]), (int)a[5], op_ptr<const int>(a[6]),                   \
+            op_ptr<const int>(a[7]), op_ptr<const int>(a[8]), (int)a[9], (int)a[10], op_ptr<TC>(a[11]), (int)a[12], H,  \
+            (int)a[16], (int)a[17], (int)a[18], op_ptr<float>(a[19]), (float)f[0], ctx->status)
+  if (a[13] == GB_BF16) PREP(bf16); else PREP(float);
+#undef PREP
+  GB_CHECK_LAUNCH("latent_prep");
+  return 1;
+}
+
+// a0 x (f32), a1 its row stride, a2 elements between heads in a row, a3 W [H, O, I], a4 its dtype, a5 out, a6 its
+// dtype, a7 its row stride, a8 elements between heads in a row, a9 rows, a10 heads, a11 O, a12 I
+GB_OP(gb_op_head_linear) {
+  const int n = (int)a[9], H = (int)a[10], O = (int)a[11], I = (int)a[12];
+  if (n <= 0) return 0;
+  const dim3 grid(gb_div_up(O, 64), gb_div_up(n, 64), H), block(256);
+#define HL(TW, TO)                                                                                                  \
+  gb_launch(head_linear_kernel<TW, TO>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], a[2],         \
+            op_ptr<const TW>(a[3]), op_ptr<TO>(a[5]), a[7], a[8], n, O, I)
+  if (a[4] == GB_BF16) { if (a[6] == GB_BF16) HL(bf16, bf16); else HL(bf16, float); }
+  else { if (a[6] == GB_BF16) HL(float, bf16); else HL(float, float); }
+#undef HL
+  GB_CHECK_LAUNCH("head_linear");
+  return 1;
+}
+
+// a0 q' [tokens, heads, r + rot] (f32), a1 pages, a2 their dtype, a3 block table, a4 its entries per request, a5 page
+// size, a6 number of pages, a7 token -> request, a8 token -> position, a9 gate logits (f32, [t, h] at a row stride) or
+// 0, a10 that stride, a11 out [tokens, heads * r] (f32), a12 its row stride, a13 tokens, a14 heads, a15 latent size,
+// a16 rotated size, a17 window (0: every earlier position); f0 scale
+GB_OP(gb_op_latent_attention) {
+  const int n = (int)a[13], H = (int)a[14], r = (int)a[15], dr = (int)a[16];
+  if (n <= 0) return 0;
+  if (r > 512) GB_FAIL(GB_ERR_ARG, "latent_attention: latent size %d (at most 512)", r);
+  const int Dk = r + dr;
+  const size_t smem = sizeof(float) * ((size_t)LA_HB * Dk + (size_t)LA_KT * (Dk + 1));
+  const dim3 grid(n, gb_div_up(H, LA_HB)), block(32 * LA_HB);
+#define LA(TC, RL)                                                                                                   \
+  do {                                                                                                               \
+    if (smem > 48 * 1024)                                                                                            \
+      GB_CUDA(cudaFuncSetAttribute(latent_attention_kernel<TC, RL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    gb_launch(latent_attention_kernel<TC, RL>, grid, block, smem, ctx->stream, op_ptr<const float>(a[0]),             \
+              op_ptr<const TC>(a[1]), op_ptr<const int>(a[3]), (int)a[4], (int)a[5], (int)a[6], op_ptr<const int>(a[7]), \
+              op_ptr<const int>(a[8]), op_ptr<const float>(a[9]), a[10], op_ptr<float>(a[11]), a[12], H, r, dr,       \
+              (float)f[0], (int)a[17], ctx->status);                                                                 \
+  } while (0)
+#define LA_RL(TC)                                                                                                    \
+  do {                                                                                                               \
+    if (r <= 32) LA(TC, 1); else if (r <= 64) LA(TC, 2); else if (r <= 128) LA(TC, 4);                              \
+    else if (r <= 256) LA(TC, 8); else LA(TC, 16);                                                                   \
+  } while (0)
+  if (a[2] == GB_BF16) LA_RL(bf16); else LA_RL(float);
+#undef LA_RL
+#undef LA
+  GB_CHECK_LAUNCH("latent_attention");
+  return 1;
+}

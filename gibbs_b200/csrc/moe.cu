@@ -1,0 +1,251 @@
+// A feed-forward that routes every token to `top` of E experts.
+//
+//  gb_op_moe_route     per token: the `top` largest router logits (ties: the lower index), their
+//                      sigmoids as weights (not renormalised), and the sigmoid of the shared expert's
+//                      gate logit; all in 32-bit
+//  gb_op_moe_sort      (token, choice) pairs ordered by expert: offsets[E + 1], the pair behind every
+//                      row, the row of every pair
+//  gb_op_moe_gather    rows[row] = weight * h[token]: the weight multiplies the expert's INPUT
+//  gb_op_moe_experts   per expert, over its rows: either act = glu(rows W_gate^T, rows W_up^T) with
+//                      clamps, or out = rows W_down^T (32-bit)
+//  gb_op_moe_combine   y[token] = sum over its choices of out[row] (+ gate * shared[token])
+//
+// A row's result does not depend on which rows share its tile (one accumulator per output walking k
+// upwards), so the order in which pairs land inside an expert's range does not matter.
+#include "hybrid.cuh"
+
+namespace {
+
+constexpr int MOE_MAX_EXPERTS = 1024;
+
+__global__ void moe_route_kernel(const float* logits, long long ld, int n, int E, int top, int shared_col, int* idx,
+                                 float* weight, float* shared_gate) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n) return;
+  const float* z = logits + (size_t)t * ld;
+  for (int k = 0; k < top; ++k) {
+    int best = -1;
+    float bv = 0.f;
+    for (int e = 0; e < E; ++e) {
+      bool taken = false;
+      for (int j = 0; j < k; ++j) taken |= idx[(size_t)t * top + j] == e;
+      if (taken) continue;
+      const float v = z[e];
+      if (best < 0 || v > bv) { best = e; bv = v; }
+    }
+    idx[(size_t)t * top + k] = best;
+    weight[(size_t)t * top + k] = hy_sigmoid(bv);
+  }
+  if (shared_gate) shared_gate[t] = hy_sigmoid(z[shared_col]);
+}
+
+// one block
+__global__ void moe_sort_kernel(const int* idx, int pairs, int E, int* offsets, int* row_pair, int* pair_row) {
+  __shared__ int count[MOE_MAX_EXPERTS + 1];
+  pdl_trigger();
+  pdl_wait();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&count[idx[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = count[e];
+      offsets[e] = at;
+      count[e] = at;
+      at += c;
+    }
+    offsets[E] = at;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int row = atomicAdd(&count[idx[p]], 1);
+    row_pair[row] = p;
+    pair_row[p] = row;
+  }
+}
+
+template <typename T>
+__global__ void moe_gather_kernel(const T* h, long long ldh, const int* row_pair, const float* weight, T* rows,
+                                  long long ldr, int pairs, int width, int top) {
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x;
+  const int p = row_pair[row];
+  const float w = weight[p];
+  const T* src = h + (size_t)(p / top) * ldh;
+  T* dst = rows + (size_t)row * ldr;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) dst[d] = from_f32<T>(w * to_f32(src[d]));
+}
+
+// The block's (expert, first row) among the tiles of all experts' ranges, or false.
+__device__ __forceinline__ bool moe_tile(const int* offsets, int E, int tile, int& e, int& r0, int& r1) {
+  for (e = 0; e < E; ++e) {
+    const int lo = offsets[e], hi = offsets[e + 1];
+    const int tiles = (hi - lo + 63) >> 6;
+    if (tile < tiles) {
+      r0 = lo + 64 * tile;
+      r1 = hi;
+      return true;
+    }
+    tile -= tiles;
+  }
+  return false;
+}
+
+// GLU: tile columns alternate gate, up, gate, up, ... of 32 features; out [rows, ff]
+template <typename TA, typename TW>
+__global__ void moe_experts_glu_kernel(const TA* rows, long long ldr, const TW* __restrict__ W, const int* offsets, int E,
+                                       TA* act, long long lda, int ff, int width, float alpha, float limit, float up_add) {
+  pdl_trigger();
+  pdl_wait();
+  int e, r0, r1;
+  if (!moe_tile(offsets, E, blockIdx.y, e, r0, r1)) return;
+  const int c0 = blockIdx.x * 32;
+  const TW* wb = W + (size_t)e * 2 * ff * width;       // [gate rows (ff) | up rows (ff)]
+  float acc[4][4];
+  int ty, tx;
+  hy_tile_64x64<TA, TW>(
+      [&](int i) -> const TA* { return r0 + i < r1 ? rows + (size_t)(r0 + i) * ldr : nullptr; },
+      [&](int j) -> const TW* {
+        const int c = c0 + (j >> 1);
+        return c < ff ? wb + (size_t)((j & 1) * ff + c) * width : nullptr;
+      },
+      width, acc, ty, tx);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int row = r0 + ty * 4 + r;
+    if (row >= r1) continue;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int col = c0 + tx * 2 + c;
+      if (col < ff)
+        act[(size_t)row * lda + col] = from_f32<TA>(hy_clamped_glu(acc[r][2 * c], acc[r][2 * c + 1], alpha, limit, up_add));
+    }
+  }
+}
+
+template <typename TA, typename TW>
+__global__ void moe_experts_down_kernel(const TA* act, long long lda, const TW* __restrict__ W, const int* offsets, int E,
+                                        float* out, long long ldo, int width, int ff) {
+  pdl_trigger();
+  pdl_wait();
+  int e, r0, r1;
+  if (!moe_tile(offsets, E, blockIdx.y, e, r0, r1)) return;
+  const int c0 = blockIdx.x * 64;
+  const TW* wb = W + (size_t)e * width * ff;
+  float acc[4][4];
+  int ty, tx;
+  hy_tile_64x64<TA, TW>(
+      [&](int i) -> const TA* { return r0 + i < r1 ? act + (size_t)(r0 + i) * lda : nullptr; },
+      [&](int j) -> const TW* { return c0 + j < width ? wb + (size_t)(c0 + j) * ff : nullptr; }, ff, acc, ty, tx);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int row = r0 + ty * 4 + r;
+    if (row >= r1) continue;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int col = c0 + tx * 4 + c;
+      if (col < width) out[(size_t)row * ldo + col] = acc[r][c];
+    }
+  }
+}
+
+__global__ void moe_combine_kernel(const float* out, long long ldo, const int* pair_row, const float* shared_gate,
+                                   const float* shared, long long lds, float* y, long long ldy, int width, int top) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float g = shared_gate ? shared_gate[t] : 0.f;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) {
+    float v = 0.f;
+    for (int k = 0; k < top; ++k) v += out[(size_t)pair_row[(size_t)t * top + k] * ldo + d];
+    if (shared) v += g * shared[(size_t)t * lds + d];
+    y[(size_t)t * ldy + d] = v;
+  }
+}
+
+}  // namespace
+
+// a0 logits (f32), a1 their row stride, a2 tokens, a3 experts, a4 top, a5 column of the shared expert's gate logit or
+// -1, a6 chosen experts [tokens, top] (int32), a7 their weights (f32), a8 shared gate [tokens] (f32) or 0
+GB_OP(gb_op_moe_route) {
+  const int n = (int)a[2], E = (int)a[3], top = (int)a[4];
+  if (n <= 0) return 0;
+  if (top < 1 || top > E) GB_FAIL(GB_ERR_ARG, "moe_route: top %d of %d experts", top, E);
+  gb_launch(moe_route_kernel, dim3(gb_div_up(n, 128)), dim3(128), 0, ctx->stream, op_ptr<const float>(a[0]), a[1], n, E,
+            top, (int)a[5], op_ptr<int>(a[6]), op_ptr<float>(a[7]), a[5] >= 0 ? op_ptr<float>(a[8]) : nullptr);
+  GB_CHECK_LAUNCH("moe_route");
+  return 1;
+}
+
+// a0 chosen experts [tokens, top], a1 tokens, a2 experts, a3 offsets [E + 1], a4 row -> pair, a5 pair -> row, a6 top
+GB_OP(gb_op_moe_sort) {
+  const int pairs = (int)(a[1] * a[6]), E = (int)a[2];
+  if (pairs <= 0) return 0;
+  if (E > MOE_MAX_EXPERTS) GB_FAIL(GB_ERR_ARG, "moe_sort: %d experts (at most %d)", E, MOE_MAX_EXPERTS);
+  gb_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, ctx->stream, op_ptr<const int>(a[0]), pairs, E, op_ptr<int>(a[3]),
+            op_ptr<int>(a[4]), op_ptr<int>(a[5]));
+  GB_CHECK_LAUNCH("moe_sort");
+  return 1;
+}
+
+// a0 h, a1 its row stride, a2 dtype (of h and rows), a3 row -> pair, a4 weights [pairs], a5 rows out, a6 their
+// stride, a7 tokens, a8 width, a9 top
+GB_OP(gb_op_moe_gather) {
+  const int pairs = (int)(a[7] * a[9]), width = (int)a[8];
+  if (pairs <= 0) return 0;
+  const dim3 grid(pairs), block(width <= 256 ? 64 : 256);
+  if (a[2] == GB_BF16)
+    gb_launch(moe_gather_kernel<bf16>, grid, block, 0, ctx->stream, op_ptr<const bf16>(a[0]), a[1], op_ptr<const int>(a[3]),
+              op_ptr<const float>(a[4]), op_ptr<bf16>(a[5]), a[6], pairs, width, (int)a[9]);
+  else
+    gb_launch(moe_gather_kernel<float>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], op_ptr<const int>(a[3]),
+              op_ptr<const float>(a[4]), op_ptr<float>(a[5]), a[6], pairs, width, (int)a[9]);
+  GB_CHECK_LAUNCH("moe_gather");
+  return 1;
+}
+
+// a0 input rows, a1 their stride, a2 their dtype, a3 weights [E, out features, in features], a4 their dtype,
+// a5 offsets [E + 1], a6 experts, a7 out, a8 its row stride, a9 tokens, a10 features out (GLU: ff), a11 features in,
+// a12 mode (0: GLU over [gate rows | up rows], out in the input's dtype; 1: plain, out f32), a13 top; f0 alpha,
+// f1 limit, f2 what is added to u
+GB_OP(gb_op_moe_experts) {
+  const int pairs = (int)(a[9] * a[13]), E = (int)a[6], n_out = (int)a[10], n_in = (int)a[11], mode = (int)a[12];
+  if (pairs <= 0) return 0;
+  const int tiles = gb_div_up(pairs, 64) + E;            // at most this many row tiles over all experts
+  const bool abf = a[2] == GB_BF16, wbf = a[4] == GB_BF16;
+  if (abf && !wbf) GB_FAIL(GB_ERR_ARG, "moe_experts: bfloat16 rows with 32-bit weights");
+#define GLU(TA, TW)                                                                                                 \
+  gb_launch(moe_experts_glu_kernel<TA, TW>, dim3(gb_div_up(n_out, 32), tiles), dim3(256), 0, ctx->stream,          \
+            op_ptr<const TA>(a[0]), a[1], op_ptr<const TW>(a[3]), op_ptr<const int>(a[5]), E, op_ptr<TA>(a[7]), a[8], \
+            n_out, n_in, (float)f[0], (float)f[1], (float)f[2])
+#define DOWN(TA, TW)                                                                                                \
+  gb_launch(moe_experts_down_kernel<TA, TW>, dim3(gb_div_up(n_out, 64), tiles), dim3(256), 0, ctx->stream,         \
+            op_ptr<const TA>(a[0]), a[1], op_ptr<const TW>(a[3]), op_ptr<const int>(a[5]), E, op_ptr<float>(a[7]),   \
+            a[8], n_out, n_in)
+  if (mode == 0) {
+    if (abf) GLU(bf16, bf16); else if (wbf) GLU(float, bf16); else GLU(float, float);
+  } else {
+    if (abf) DOWN(bf16, bf16); else if (wbf) DOWN(float, bf16); else DOWN(float, float);
+  }
+#undef GLU
+#undef DOWN
+  GB_CHECK_LAUNCH("moe_experts");
+  return 1;
+}
+
+// a0 expert outputs by row (f32), a1 their stride, a2 pair -> row, a3 shared gate [tokens] or 0, a4 shared expert's
+// output (f32) or 0, a5 its row stride, a6 y (f32), a7 its row stride, a8 tokens, a9 width, a10 top
+GB_OP(gb_op_moe_combine) {
+  const int n = (int)a[8], width = (int)a[9];
+  if (n <= 0) return 0;
+  gb_launch(moe_combine_kernel, dim3(n), dim3(width <= 256 ? 64 : 256), 0, ctx->stream, op_ptr<const float>(a[0]), a[1],
+            op_ptr<const int>(a[2]), op_ptr<const float>(a[3]), op_ptr<const float>(a[4]), a[5], op_ptr<float>(a[6]), a[7],
+            width, (int)a[10]);
+  GB_CHECK_LAUNCH("moe_combine");
+  return 1;
+}

@@ -1,0 +1,186 @@
+// Norms over rows of the 32-bit residual stream and the small element-wise kernels around them.
+//
+//  gb_op_row_norm        out = norm(x[rows]) * gain, layer norm (mean taken off, variance as the mean
+//                        of squared deviations) or RMS norm, statistics in 32-bit
+//  gb_op_norm_add        x += norm(y) * gain: the norm AFTER a sublayer, added into the stream
+//  gb_op_clamped_glu     out = g' * sigmoid(alpha g') * (u' + up_add) for rows [g | u] with clamps
+//  gb_op_gelu_mul_rows   g = gelu_tanh(g) * table[id, offset : offset + dim] (a per-token input)
+//  gb_op_gated_group_norm  out = rmsnorm_in_groups(y * silu(z)) * gain
+#include "hybrid.cuh"
+
+namespace {
+
+enum { NORM_LAYER = 0, NORM_RMS = 1 };
+
+// mean and 1/sqrt(var + eps) of a row of `dim` floats; every thread of the block gets both.
+__device__ __forceinline__ void row_stats(const float* row, int dim, int kind, float eps, float* scratch, float& mean,
+                                          float& rstd) {
+  mean = 0.f;
+  if (kind == NORM_LAYER) {
+    float s = 0.f;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) s += row[d];
+    mean = block_sum(s, scratch) / (float)dim;
+  }
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    const float v = row[d] - mean;
+    ss += v * v;
+  }
+  rstd = 1.0f / sqrtf(block_sum(ss, scratch) / (float)dim + eps);
+}
+
+template <typename TO>
+__global__ void row_norm_kernel(const float* x, long long ldx, const float* __restrict__ gain, TO* out, const int* rows,
+                                int dim, int kind, float eps) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const float* row = x + (size_t)(rows ? rows[r] : r) * ldx;
+  float mean, rstd;
+  row_stats(row, dim, kind, eps, scratch, mean, rstd);
+  TO* o = out + (size_t)r * dim;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) o[d] = from_f32<TO>((row[d] - mean) * rstd * gain[d]);
+}
+
+__global__ void norm_add_kernel(float* x, long long ldx, const float* y, long long ldy, const float* __restrict__ gain,
+                                int dim, int kind, float eps) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  const float* row = y + (size_t)blockIdx.x * ldy;
+  float mean, rstd;
+  row_stats(row, dim, kind, eps, scratch, mean, rstd);
+  float* o = x + (size_t)blockIdx.x * ldx;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) o[d] += (row[d] - mean) * rstd * gain[d];
+}
+
+template <typename TO>
+__global__ void clamped_glu_kernel(const float* gu, long long ld, TO* out, long long ldo, int n, int inner, float alpha,
+                                   float limit, float up_add) {
+  pdl_trigger();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)n * inner) return;
+  const int t = (int)(i / inner), c = (int)(i - (long long)t * inner);
+  const float* row = gu + (size_t)t * ld;
+  out[(size_t)t * ldo + c] = from_f32<TO>(hy_clamped_glu(row[c], row[inner + c], alpha, limit, up_add));
+}
+
+template <typename TT>
+__global__ void gelu_mul_rows_kernel(float* g, long long ld, const TT* __restrict__ table, long long ldt, int offset,
+                                     const int* ids, int n, int dim, int vocab) {
+  pdl_trigger();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)n * dim) return;
+  const int t = (int)(i / dim), c = (int)(i - (long long)t * dim);
+  const int id = ids[t];
+  const float e = (id >= 0 && id < vocab) ? to_f32(table[(size_t)id * ldt + offset + c]) : 0.f;
+  float* p = g + (size_t)t * ld + c;
+  *p = hy_gelu_tanh(*p) * e;
+}
+
+// one block per (row, group)
+template <typename TO>
+__global__ void gated_group_norm_kernel(const float* y, long long ldy, const float* z, long long ldz,
+                                        const float* __restrict__ gain, TO* out, long long ldo, int inner, int groups,
+                                        float eps) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, g = blockIdx.y;
+  const int width = inner / groups, c0 = g * width;
+  const float* yr = y + (size_t)t * ldy + c0;
+  const float* zr = z + (size_t)t * ldz + c0;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) {
+    const float v = yr[d] * hy_silu(zr[d]);
+    ss += v * v;
+  }
+  const float rstd = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+  TO* o = out + (size_t)t * ldo + c0;
+  for (int d = threadIdx.x; d < width; d += blockDim.x)
+    o[d] = from_f32<TO>(yr[d] * hy_silu(zr[d]) * rstd * gain[c0 + d]);
+}
+
+inline int norm_threads(int dim) { return dim <= 256 ? 64 : dim <= 1024 ? 128 : 256; }
+
+}  // namespace
+
+// a0 x (f32), a1 its row stride, a2 gain, a3 out [rows, dim], a4 out dtype, a5 row list (int32) or 0, a6 rows,
+// a7 dim, a8 kind (0 layer norm, 1 RMS norm); f0 eps
+GB_OP(gb_op_row_norm) {
+  const int n = (int)a[6], dim = (int)a[7], kind = (int)a[8];
+  if (n <= 0) return 0;
+  if (kind != NORM_LAYER && kind != NORM_RMS) GB_FAIL(GB_ERR_ARG, "row_norm: kind %d", kind);
+  const dim3 grid(n), block(norm_threads(dim));
+  if (a[4] == GB_BF16)
+    gb_launch(row_norm_kernel<bf16>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], op_ptr<const float>(a[2]),
+              op_ptr<bf16>(a[3]), op_ptr<const int>(a[5]), dim, kind, (float)f[0]);
+  else
+    gb_launch(row_norm_kernel<float>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], op_ptr<const float>(a[2]),
+              op_ptr<float>(a[3]), op_ptr<const int>(a[5]), dim, kind, (float)f[0]);
+  GB_CHECK_LAUNCH("row_norm");
+  return 1;
+}
+
+// a0 x (f32, the stream), a1 its row stride, a2 y (f32), a3 its row stride, a4 gain, a5 rows, a6 dim, a7 kind; f0 eps
+GB_OP(gb_op_norm_add) {
+  const int n = (int)a[5], dim = (int)a[6], kind = (int)a[7];
+  if (n <= 0) return 0;
+  if (kind != NORM_LAYER && kind != NORM_RMS) GB_FAIL(GB_ERR_ARG, "norm_add: kind %d", kind);
+  gb_launch(norm_add_kernel, dim3(n), dim3(norm_threads(dim)), 0, ctx->stream, op_ptr<float>(a[0]), a[1],
+            op_ptr<const float>(a[2]), a[3], op_ptr<const float>(a[4]), dim, kind, (float)f[0]);
+  GB_CHECK_LAUNCH("norm_add");
+  return 1;
+}
+
+// a0 rows [g | u] (f32), a1 their stride, a2 out [n, inner], a3 out dtype, a4 its row stride, a5 rows, a6 inner;
+// f0 alpha, f1 limit, f2 what is added to u
+GB_OP(gb_op_clamped_glu) {
+  const int n = (int)a[5], inner = (int)a[6];
+  if (n <= 0) return 0;
+  const dim3 grid(gb_div_up((long long)n * inner, 256)), block(256);
+  if (a[3] == GB_BF16)
+    gb_launch(clamped_glu_kernel<bf16>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], op_ptr<bf16>(a[2]),
+              a[4], n, inner, (float)f[0], (float)f[1], (float)f[2]);
+  else
+    gb_launch(clamped_glu_kernel<float>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], op_ptr<float>(a[2]),
+              a[4], n, inner, (float)f[0], (float)f[1], (float)f[2]);
+  GB_CHECK_LAUNCH("clamped_glu");
+  return 1;
+}
+
+// a0 g (f32, in place), a1 its row stride, a2 table, a3 its dtype, a4 its row stride, a5 first column, a6 token ids,
+// a7 rows, a8 dim, a9 rows of the table
+GB_OP(gb_op_gelu_mul_rows) {
+  const int n = (int)a[7], dim = (int)a[8];
+  if (n <= 0) return 0;
+  const dim3 grid(gb_div_up((long long)n * dim, 256)), block(256);
+  if (a[3] == GB_BF16)
+    gb_launch(gelu_mul_rows_kernel<bf16>, grid, block, 0, ctx->stream, op_ptr<float>(a[0]), a[1], op_ptr<const bf16>(a[2]),
+              a[4], (int)a[5], op_ptr<const int>(a[6]), n, dim, (int)a[9]);
+  else
+    gb_launch(gelu_mul_rows_kernel<float>, grid, block, 0, ctx->stream, op_ptr<float>(a[0]), a[1], op_ptr<const float>(a[2]),
+              a[4], (int)a[5], op_ptr<const int>(a[6]), n, dim, (int)a[9]);
+  GB_CHECK_LAUNCH("gelu_mul_rows");
+  return 1;
+}
+
+// a0 y (f32), a1 its row stride, a2 z (f32), a3 its row stride, a4 gain [inner], a5 out, a6 out dtype, a7 its row
+// stride, a8 rows, a9 inner, a10 groups; f0 eps
+GB_OP(gb_op_gated_group_norm) {
+  const int n = (int)a[8], inner = (int)a[9], groups = (int)a[10];
+  if (n <= 0) return 0;
+  if (groups <= 0 || inner % groups) GB_FAIL(GB_ERR_ARG, "gated_group_norm: %d columns in %d groups", inner, groups);
+  const dim3 grid(n, groups), block(norm_threads(inner / groups));
+  if (a[6] == GB_BF16)
+    gb_launch(gated_group_norm_kernel<bf16>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1],
+              op_ptr<const float>(a[2]), a[3], op_ptr<const float>(a[4]), op_ptr<bf16>(a[5]), a[7], inner, groups, (float)f[0]);
+  else
+    gb_launch(gated_group_norm_kernel<float>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1],
+              op_ptr<const float>(a[2]), a[3], op_ptr<const float>(a[4]), op_ptr<float>(a[5]), a[7], inner, groups, (float)f[0]);
+  GB_CHECK_LAUNCH("gated_group_norm");
+  return 1;
+}

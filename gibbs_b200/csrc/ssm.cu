@@ -1,0 +1,162 @@
+// A selective state-space mixer (the scalar-decay, multi-head form) over a ragged batch of prompt
+// portions and single decoded tokens, with per-request state in slots.
+//
+//  gb_op_causal_conv_silu   per channel: silu(bias + sum_j taps[c][j] * in[t - (K-1) + j]); the K-1 inputs
+//                           before a portion come from the request's slot (zeros for a new request), and
+//                           the slot then receives the portion's last K-1 inputs.
+//  gb_op_ssm_scan           per head h (group g = h / (heads/groups)), token after token:
+//                             dt = softplus(dt_raw + dt_bias[h]);  a = exp(-exp(A_log[h]) * dt)
+//                             S  = a * S + dt * B_t x_t^T          (S: [state, head_dim], 32-bit, in the slot)
+//                             y_t = S^T C_t + D[h] * x_t
+//                           Everything here is 32-bit.
+//
+// State layout in a slot: conv [K-1][channels] (oldest first); recurrence [heads][head_dim][state].
+#include "hybrid.cuh"
+
+namespace {
+
+__global__ void causal_conv_silu_kernel(const float* in, long long ld, const float* __restrict__ taps,
+                                        const float* __restrict__ bias, const float* state, long long slot_stride,
+                                        const int* slot_ids, const int* tok_req, const int* q_start, float* out,
+                                        long long ldo, int n, int C, int K) {
+  pdl_trigger();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)n * C) return;
+  const int t = (int)(i / C), c = (int)(i - (long long)t * C);
+  const int r = tok_req[t];
+  const int first = q_start[r];
+  const int li = t - first;                               // index within the portion
+  const float* st = state + (size_t)slot_ids[r] * slot_stride;
+  float acc = bias ? bias[c] : 0.f;
+  for (int j = 0; j < K; ++j) {
+    const int s = li - (K - 1) + j;
+    const float v = s >= 0 ? in[(size_t)(first + s) * ld + c] : st[(size_t)(K - 1 + s) * C + c];
+    acc = fmaf(taps[(size_t)c * K + j], v, acc);
+  }
+  out[(size_t)t * ldo + c] = hy_silu(acc);
+}
+
+// one thread per (request, channel): the slot's K-1 rows become the last K-1 inputs seen
+__global__ void conv_state_update_kernel(const float* in, long long ld, float* state, long long slot_stride,
+                                         const int* slot_ids, const int* q_start, const int* q_len, int R, int C, int K) {
+  pdl_trigger();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)R * C) return;
+  const int r = (int)(i / C), c = (int)(i - (long long)r * C);
+  const int first = q_start[r], len = q_len[r];
+  float* st = state + (size_t)slot_ids[r] * slot_stride;
+  for (int j = 0; j < K - 1; ++j) {                        // ascending: row j reads row j + len (> j) or the portion
+    const int s = len - (K - 1) + j;
+    st[(size_t)j * C + c] = s >= 0 ? in[(size_t)(first + s) * ld + c] : st[(size_t)(K - 1 + s) * C + c];
+  }
+}
+
+// Block: 4 warps, each with PC columns p of one head; lane l holds S[p][n] for n = l + 32 i, i < NPL.
+constexpr int SCAN_WARPS = 4, SCAN_PC = 2;
+
+template <int NPL>
+__global__ void ssm_scan_kernel(const float* xbc, long long ld, const float* dt_raw, long long ld_dt,
+                                const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                                const float* __restrict__ dskip, float* state, long long slot_stride,
+                                const int* slot_ids, const int* q_start, const int* q_len, float* y, long long ldy, int H,
+                                int P, int N, int G) {
+  pdl_trigger();
+  const int r = blockIdx.x, h = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int p0 = (blockIdx.z * SCAN_WARPS + warp) * SCAN_PC;
+  const int g = h / (H / G);
+  const int inner = H * P;
+  const float bias = dt_bias[h], neg_a = -expf(a_log[h]), dsk = dskip[h];
+  const int first = q_start[r], len = q_len[r];
+  float* S = state + (size_t)slot_ids[r] * slot_stride + (size_t)h * P * N;
+  pdl_wait();
+  if (p0 >= P) return;
+  float s[SCAN_PC][NPL];
+#pragma unroll
+  for (int c = 0; c < SCAN_PC; ++c)
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int n = lane + 32 * i;
+      s[c][i] = (p0 + c < P && n < N) ? S[(size_t)(p0 + c) * N + n] : 0.f;
+    }
+  for (int t = 0; t < len; ++t) {
+    const float* row = xbc + (size_t)(first + t) * ld;
+    const float dt = hy_softplus(dt_raw[(size_t)(first + t) * ld_dt + h] + bias);
+    const float decay = expf(neg_a * dt);
+    float bv[NPL], cv[NPL];
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int n = lane + 32 * i;
+      bv[i] = n < N ? row[inner + g * N + n] * dt : 0.f;
+      cv[i] = n < N ? row[inner + (G + g) * N + n] : 0.f;
+    }
+#pragma unroll
+    for (int c = 0; c < SCAN_PC; ++c) {
+      const int p = p0 + c;
+      const float xv = p < P ? row[h * P + p] : 0.f;
+      float part = 0.f;
+#pragma unroll
+      for (int i = 0; i < NPL; ++i) {
+        s[c][i] = fmaf(decay, s[c][i], bv[i] * xv);
+        part = fmaf(s[c][i], cv[i], part);
+      }
+      part = warp_sum(part);
+      if (lane == 0 && p < P) y[(size_t)(first + t) * ldy + h * P + p] = part + dsk * xv;
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < SCAN_PC; ++c)
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int n = lane + 32 * i;
+      if (p0 + c < P && n < N) S[(size_t)(p0 + c) * N + n] = s[c][i];
+    }
+}
+
+}  // namespace
+
+// a0 in (f32; the convolved columns of a wider row), a1 its row stride, a2 taps [C, K], a3 bias [C] or 0, a4 conv
+// state of slot 0, a5 elements between slots, a6 slot ids, a7 token -> request, a8 first row per request, a9 rows per
+// request, a10 out (f32), a11 its row stride, a12 tokens, a13 channels, a14 taps per channel, a15 requests
+GB_OP(gb_op_causal_conv_silu) {
+  const int n = (int)a[12], C = (int)a[13], K = (int)a[14], R = (int)a[15];
+  if (n <= 0) return 0;
+  if (K < 1) GB_FAIL(GB_ERR_ARG, "causal_conv_silu: %d taps", K);
+  gb_launch(causal_conv_silu_kernel, dim3(gb_div_up((long long)n * C, 256)), dim3(256), 0, ctx->stream,
+            op_ptr<const float>(a[0]), a[1], op_ptr<const float>(a[2]), op_ptr<const float>(a[3]), op_ptr<const float>(a[4]),
+            a[5], op_ptr<const int>(a[6]), op_ptr<const int>(a[7]), op_ptr<const int>(a[8]), op_ptr<float>(a[10]), a[11], n,
+            C, K);
+  GB_CHECK_LAUNCH("causal_conv_silu");
+  if (K == 1) return 1;
+  gb_launch(conv_state_update_kernel, dim3(gb_div_up((long long)R * C, 256)), dim3(256), 0, ctx->stream,
+            op_ptr<const float>(a[0]), a[1], op_ptr<float>(a[4]), a[5], op_ptr<const int>(a[6]), op_ptr<const int>(a[8]),
+            op_ptr<const int>(a[9]), R, C, K);
+  GB_CHECK_LAUNCH("conv_state_update");
+  return 2;
+}
+
+// a0 rows [x | B | C] after the convolution (f32), a1 their stride, a2 dt before the bias (f32; a column of a wider
+// row), a3 its row stride, a4 dt_bias [H], a5 A_log [H], a6 D [H], a7 recurrent state of slot 0, a8 elements between
+// slots, a9 slot ids, a10 first row per request, a11 rows per request, a12 y (f32), a13 its row stride, a14 requests,
+// a15 heads, a16 head_dim, a17 state size, a18 groups
+GB_OP(gb_op_ssm_scan) {
+  const int R = (int)a[14], H = (int)a[15], P = (int)a[16], N = (int)a[17], G = (int)a[18];
+  if (R <= 0) return 0;
+  if (G <= 0 || H % G) GB_FAIL(GB_ERR_ARG, "ssm_scan: %d heads in %d groups", H, G);
+  if (N > 256) GB_FAIL(GB_ERR_ARG, "ssm_scan: state size %d (at most 256)", N);
+  const dim3 grid(R, H, gb_div_up(P, SCAN_WARPS * SCAN_PC)), block(32 * SCAN_WARPS);
+#define SCAN_LAUNCH(NPL)                                                                                              \
+  gb_launch(ssm_scan_kernel<NPL>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], op_ptr<const float>(a[2]), \
+            a[3], op_ptr<const float>(a[4]), op_ptr<const float>(a[5]), op_ptr<const float>(a[6]), op_ptr<float>(a[7]),   \
+            a[8], op_ptr<const int>(a[9]), op_ptr<const int>(a[10]), op_ptr<const int>(a[11]), op_ptr<float>(a[12]),    \
+            a[13], H, P, N, G)
+  if (N <= 32) SCAN_LAUNCH(1);
+  else if (N <= 64) SCAN_LAUNCH(2);
+  else if (N <= 128) SCAN_LAUNCH(4);
+  else SCAN_LAUNCH(8);
+#undef SCAN_LAUNCH
+  GB_CHECK_LAUNCH("ssm_scan");
+  return 1;
+}

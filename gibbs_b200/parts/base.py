@@ -17,12 +17,17 @@ Categories and what each must implement:
   position    ``rotary() -> Rotary | None`` (tables a mixer's kernel applies)
               and ``embed(x_f32, step)`` (an in-place hook on the embedded
               tokens; default nothing).
-  mixer       ``cache_needs() -> [PagedKV | SlotState, ...]`` and
+  mixer       ``cache_needs() -> [PagedKV | PagedRows | SlotState, ...]`` and
               ``forward(h, residual, step, caches)`` which ADDS the mixer's
               output into the ``Residual`` stream (``residual.add_(y)``, or a
               projection called with ``out=residual, accumulate=True``);
               ``caches`` holds one view per need.
   feed_forward ``forward(h, residual, step)``, adding likewise.
+  token_input ``forward(x, step)``: adds to the stream something that depends on the
+              tokens' ids as well (a per-layer table looked up by token).
+  A mixer or feed-forward with ``writes_branch`` (``parts.runner.BranchPart``) can also
+  WRITE its output into a float32 tensor given in place of the stream, for arrangements
+  that put a norm between the sublayer and the residual sum.
   block       an arrangement of parts around the residual stream.  Its class
               names the roles it is made of (``ROLES``: (role, category) pairs);
               a plan's layer gives one part per role; the block is built from
@@ -75,6 +80,15 @@ class PagedKV:
     @property
     def value_dim(self) -> int:
         return self.head_dim if self.v_head_dim is None else self.v_head_dim
+
+
+@dataclass(frozen=True)
+class PagedRows:
+    """One row of ``width`` values per position (or per position of the last ``window``),
+    in pages [n_pages, page_size, width]: what a mixer keeps that is neither a key nor a
+    value per head (a compressed latent from which both derive, say)."""
+    width: int
+    window: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -310,7 +324,7 @@ class Block:
 
 # ---------------------------------------------------------------------------
 _REGISTRY: dict[tuple[str, str], Any] = {}
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "token_input", "block", "embedding", "head")
 
 
 def register_part(category: str, kind: str, cls) -> None:

@@ -1,7 +1,10 @@
 """Arrangements of norm, mixer and feed-forward around the residual stream."""
 from __future__ import annotations
 
+import torch
+
 from .base import Block, plan_ops_of, register_part
+from .runner import Eager, Planned, stream_tensor
 
 
 class PreNormResidual(Block):
@@ -35,3 +38,50 @@ class PreNormResidual(Block):
 
 
 register_part("block", "prenorm_residual", PreNormResidual)
+
+
+class SandwichResidual(Block):
+    """A norm in front of AND behind every sublayer:
+
+        x += post_norm(mixer(norm(x)));  x += post_norm(ffn(norm(x)));  token_input(x)
+
+    The feed-forward (with its two norms) and the token input are optional.  Sublayers write
+    their output for the norm behind them (``parts.runner.BranchPart``); the norms behind are
+    ``RowNorm`` kinds, whose ``add_normed`` adds into the stream."""
+    ROLES = (("mixer_norm", "norm"), ("mixer", "mixer"), ("mixer_post_norm", "norm"), ("ffn_norm", "norm"),
+             ("ffn", "feed_forward"), ("ffn_post_norm", "norm"), ("token_input", "token_input"))
+    OPTIONAL_ROLES = ("ffn_norm", "ffn", "ffn_post_norm", "token_input")
+
+    def __init__(self, parts, rt, params=None):
+        super().__init__(parts, rt, params)
+        have = set(self.parts)
+        if len(have & {"ffn_norm", "ffn", "ffn_post_norm"}) not in (0, 3):
+            raise ValueError("a feed-forward comes with the norm in front of it and the norm behind it")
+        for role in ("mixer", "ffn"):
+            if role in have and not getattr(self.parts[role], "writes_branch", False):
+                raise ValueError(f"the {role} of this arrangement must be able to write its output for the norm "
+                                 f"behind it; {type(self.parts[role]).__name__} only adds into the stream")
+        for role in ("mixer_post_norm", "ffn_post_norm"):
+            if role in have and not hasattr(self.parts[role], "add_normed"):
+                raise ValueError(f"the {role} must be a norm that can add into the stream (a RowNorm kind)")
+
+    def _run(self, rn, x, caches, h_of):
+        hidden = x.shape[1]
+        y = rn.buffer("branch", hidden, torch.float32)
+        self.mixer.run(rn, h_of(self.mixer_norm), y, self.caches_of("mixer", caches))
+        self.mixer_post_norm.add_normed(rn, x, y)
+        if "ffn" in self.parts:
+            self.ffn.run(rn, h_of(self.ffn_norm), y, None)
+            self.ffn_post_norm.add_normed(rn, x, y)
+        if "token_input" in self.parts:
+            self.token_input.run(rn, x)
+
+    def forward(self, x, step, caches):
+        rn, xt = Eager(self.rt, step), stream_tensor(x)
+        self._run(rn, xt, caches, lambda norm: norm.forward(xt))
+
+    def plan_ops(self, plan, caches):
+        self._run(Planned(plan), plan.residual, caches, lambda norm: plan_ops_of(norm)(plan))
+
+
+register_part("block", "sandwich_residual", SandwichResidual)

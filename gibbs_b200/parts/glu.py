@@ -1,0 +1,138 @@
+"""Gated feed-forwards with clamps, dense and routed.
+
+Dense (``clamped_glu``):
+
+    g = min(W_gate h, limit),  u = clamp(W_up h, -limit, limit)
+    out = W_down (g * sigmoid(alpha * g) * (u + up_add))
+
+Routed (``routed_glu``): E such experts without biases, of which every token
+uses ``top``.  Router logits z = W_router h and scores s = sigmoid(z) are 32-bit;
+the ``top`` largest scores choose the experts; a chosen expert's weight is its
+score (not renormalised) and multiplies the expert's INPUT: out = sum_e
+expert_e(s_e * h).  An optional shared expert runs for every token and is added
+times sigmoid(W_sg h), one number per token.  Tokens are ordered by expert on
+the device (no host round trip), the experts' products run over the ragged row
+ranges (csrc/moe.cu).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..ops import hybrid
+from .base import FeedForward, TensorDecl, VECTOR, register_part, tensor_bytes
+from .runner import BranchPart, Runner, keep
+
+
+class ClampedGLU(BranchPart, FeedForward):
+    @classmethod
+    def declare(cls, params):
+        h, f = params["hidden"], params["inner"]
+        return {"gate": TensorDecl.of(f, h), "up": TensorDecl.of(f, h), "down": TensorDecl.of(h, f)}
+
+    def __init__(self, params, tensors, rt):
+        super().__init__(params, tensors, rt)
+        self.hidden, self.inner = int(params["hidden"]), int(params["inner"])
+        self.limit = float(params["limit"])
+        self.alpha, self.up_add = float(params.get("alpha", 1.702)), float(params.get("up_add", 1.0))
+        if tensors["gate"].dtype != tensors["up"].dtype:
+            raise ValueError("gate and up projections are stored in different dtypes")
+        self.gate_up = torch.cat([tensors["gate"], tensors["up"]], 0).contiguous()
+        self.down = tensors["down"].contiguous()
+
+    def kernel_libraries(self):
+        return tuple(set(ops.linear_libraries(self.gate_up.dtype, self.rt.dtype)) | {"core", hybrid.LIBRARY})
+
+    def run(self, rn: Runner, h, out, caches=None):
+        gu = rn.buffer("glu_gate_up", 2 * self.inner, torch.float32)
+        rn.linear(h, self.gate_up, None, gu)
+        act = rn.buffer("glu_act", self.inner)
+        rn.op("clamped_glu", [gu.data_ptr(), gu.stride(0), act.data_ptr(), ops.dtype_code(act.dtype), act.stride(0),
+                              rn.N, self.inner], [self.alpha, self.limit, self.up_add])
+        rn.linear(act, self.down, None, out)
+
+
+class RoutedGLU(BranchPart, FeedForward):
+    @classmethod
+    def declare(cls, params):
+        h, E, f = params["hidden"], params["experts"], params["expert_inner"]
+        d = {"router": TensorDecl.of(E, h, role=VECTOR)}
+        for e in range(E):
+            d.update({f"e{e}.gate": TensorDecl.of(f, h), f"e{e}.up": TensorDecl.of(f, h), f"e{e}.down": TensorDecl.of(h, f)})
+        if params.get("shared_inner"):
+            s = params["shared_inner"]
+            d.update({"shared.gate": TensorDecl.of(s, h), "shared.up": TensorDecl.of(s, h),
+                      "shared.down": TensorDecl.of(h, s), "shared.sg": TensorDecl.of(1, h, role=VECTOR)})
+        return d
+
+    def __init__(self, params, tensors, rt):
+        super().__init__(params, tensors, rt)
+        p = params
+        self.hidden, self.E, self.top, self.inner = int(p["hidden"]), int(p["experts"]), int(p["top"]), int(p["expert_inner"])
+        self.limit = float(p["expert_limit"])
+        self.alpha, self.up_add = float(p.get("alpha", 1.702)), float(p.get("up_add", 1.0))
+        if not 1 <= self.top <= self.E:
+            raise ValueError(f"top {self.top} of {self.E} experts")
+        E = self.E
+        self.w_gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], 0) for e in range(E)]).contiguous()
+        self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(E)]).contiguous()
+        self.shared = None
+        rows = [tensors["router"].to(torch.float32)]
+        if p.get("shared_inner"):
+            self.shared = ClampedGLU({"hidden": self.hidden, "inner": int(p["shared_inner"]), "limit": float(p["shared_limit"]),
+                                      "alpha": self.alpha, "up_add": self.up_add},
+                                     {k: tensors["shared." + k] for k in ("gate", "up", "down")}, rt)
+            rows.append(tensors["shared.sg"].to(torch.float32).reshape(1, self.hidden))
+        # the router and the shared expert's gate in one small 32-bit product
+        self.w_router = torch.cat(rows, 0).contiguous()
+
+    def kernel_libraries(self):
+        return tuple(set(ops.linear_libraries(self.w_down.dtype, self.rt.dtype)) | {"core", hybrid.LIBRARY})
+
+    def step_weight_bytes(self, n_tokens: int, seen: set) -> int:
+        """A step reads the router, the shared expert and the experts its tokens choose:
+        at most n_tokens * top of them."""
+        per_expert = (self.w_gate_up[0].numel() + self.w_down[0].numel()) * self.w_down.element_size()
+        total = min(self.E, n_tokens * self.top) * per_expert + self.w_router.numel() * 4
+        seen.update((self.w_gate_up.data_ptr(), self.w_down.data_ptr(), self.w_router.data_ptr()))
+        if self.shared is not None:
+            total += tensor_bytes(self.shared, seen)
+        return total
+
+    def run(self, rn: Runner, h, out, caches=None):
+        E, top, d, f = self.E, self.top, self.hidden, self.inner
+        shared = self.shared is not None
+        logits = rn.buffer("moe_logits", E + (1 if shared else 0), torch.float32)
+        rn.linear(h, self.w_router, None, logits)
+        idx = rn.buffer("moe_choice", top, torch.int32)
+        wts = rn.buffer("moe_weight", top, torch.float32)
+        sg = rn.buffer("moe_shared_gate", 1, torch.float32)
+        rn.op("moe_route", [logits.data_ptr(), logits.stride(0), rn.N, E, top, E if shared else -1, idx.data_ptr(),
+                            wts.data_ptr(), sg.data_ptr()])
+        offsets = rn.buffer("moe_offsets", E + 1, torch.int32, fixed_rows=1)
+        row_pair = rn.buffer("moe_row_pair", top, torch.int32)
+        pair_row = rn.buffer("moe_pair_row", top, torch.int32)
+        rn.op("moe_sort", [idx.data_ptr(), rn.N, E, offsets.data_ptr(), row_pair.data_ptr(), pair_row.data_ptr(), top])
+        rows = rn.buffer("moe_rows", d, per_token=top)
+        rn.op("moe_gather", [h.data_ptr(), h.stride(0), ops.dtype_code(h.dtype), row_pair.data_ptr(), wts.data_ptr(),
+                             rows.data_ptr(), rows.stride(0), rn.N, d, top])
+        act = rn.buffer("moe_act", f, per_token=top)
+        wdt = ops.dtype_code(self.w_down.dtype)
+        rn.op("moe_experts", [rows.data_ptr(), rows.stride(0), ops.dtype_code(rows.dtype), keep(rn, self.w_gate_up), wdt,
+                              offsets.data_ptr(), E, act.data_ptr(), act.stride(0), rn.N, f, d, 0, top],
+              [self.alpha, self.limit, self.up_add], label="moe_experts:gate_up")
+        eout = rn.buffer("moe_expert_out", d, torch.float32, per_token=top)
+        rn.op("moe_experts", [act.data_ptr(), act.stride(0), ops.dtype_code(act.dtype), keep(rn, self.w_down), wdt,
+                              offsets.data_ptr(), E, eout.data_ptr(), eout.stride(0), rn.N, d, f, 1, top],
+              label="moe_experts:down")
+        sh = None
+        if shared:
+            sh = rn.buffer("moe_shared_out", d, torch.float32)
+            self.shared.run(rn, h, sh)
+        rn.op("moe_combine", [eout.data_ptr(), eout.stride(0), pair_row.data_ptr(), sg.data_ptr() if shared else 0,
+                              sh.data_ptr() if shared else 0, sh.stride(0) if shared else 0, out.data_ptr(),
+                              out.stride(0), rn.N, d, top])
+
+
+register_part("feed_forward", "clamped_glu", ClampedGLU)
+register_part("feed_forward", "routed_glu", RoutedGLU)

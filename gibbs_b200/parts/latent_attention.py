@@ -1,0 +1,107 @@
+"""Attention over a compressed key/value cache ("latent attention"), with an
+output gate per head and an optional sliding window.
+
+For a token with mixer input h (H heads; per head ``dim`` unrotated and
+``rot_dim`` rotated query/key entries, values of ``vdim``, latent of ``kv_rank``):
+
+    q            = W_q h                      per head [unrotated | rotated]
+    [l | kr]     = W_dkv h                    kv_rank + rot_dim entries
+    c            = rmsnorm(l) * gain          the latent; kr is ONE rotated key part for all heads
+    k_h          = [W_uk,h c | rot(kr)],  v_h = W_uv,h c
+    o_h          = sigmoid(W_g h)_h * sum_j softmax_j(scale * q_h . k_h,j) v_h,j
+    out          = W_o [o_1 .. o_H]
+
+Only [c | rot(kr)] is cached, one row per position (``PagedRows``).  The kernels
+use the absorbed form: W_uk,h is moved to the query side and W_uv,h behind the
+weighted sum of latents, so that prompt portions and decoded tokens alike read
+nothing but cache rows (csrc/latent_attention.cu).  Position i sees the
+positions j with 0 <= i - j < window (all earlier ones without a window).  The
+rotation turns the first ``rot_dims`` entries of a rotated part in adjacent
+pairs by pos * base^(-2i / rot_dims).
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..ops import hybrid
+from .base import Mixer, PagedRows, TensorDecl, VECTOR, register_part
+from .runner import BranchPart, Runner, keep
+
+
+class LatentAttention(BranchPart, Mixer):
+    @classmethod
+    def declare(cls, params):
+        d, H = params["hidden"], params["heads"]
+        dn, dr, dv, r = params["dim"], params["rot_dim"], params["vdim"], params["kv_rank"]
+        return {"q": TensorDecl.of(H * (dn + dr), d), "dkv": TensorDecl.of(r + dr, d),
+                "dkv.norm": TensorDecl.of(r, role=VECTOR), "uk": TensorDecl.of(H * dn, r),
+                "uv": TensorDecl.of(H * dv, r), "g": TensorDecl.of(H, d), "o": TensorDecl.of(d, H * dv)}
+
+    def __init__(self, params, tensors, rt):
+        super().__init__(params, tensors, rt)
+        p = params
+        self.hidden, self.heads = int(p["hidden"]), int(p["heads"])
+        self.dn, self.dr, self.dv, self.r = int(p["dim"]), int(p["rot_dim"]), int(p["vdim"]), int(p["kv_rank"])
+        self.window = int(p["window"]) if p.get("window") else None
+        self.scale, self.eps = float(p["scale"]), float(p["eps"])
+        self.rot_dims = int(p.get("rot_dims", self.dr))
+        if self.rot_dims % 2 or not 0 <= self.rot_dims <= self.dr:
+            raise ValueError(f"{self.rot_dims} rotated dimensions must be even and at most rot_dim {self.dr}")
+        H = self.heads
+        # one product for [q | latent, rotated key | gate logits]
+        self.fused = torch.cat([tensors["q"], tensors["dkv"], tensors["g"]], 0).contiguous()
+        self.dkv_col, self.gate_col = H * (self.dn + self.dr), H * (self.dn + self.dr) + self.r + self.dr
+        # per head: W_uk,h^T as [kv_rank, dim] (applied to the query), W_uv,h as [vdim, kv_rank]
+        self.uk_t = tensors["uk"].reshape(H, self.dn, self.r).transpose(1, 2).contiguous()
+        self.uv = tensors["uv"].reshape(H, self.dv, self.r).contiguous()
+        self.latent_gain = tensors["dkv.norm"].to(torch.float32).contiguous()
+        self.o = tensors["o"].contiguous()
+        i = np.arange(self.rot_dims // 2, dtype=np.float64)
+        inv = np.power(float(p["rot_base"]), -2.0 * i / max(self.rot_dims, 1))
+        self.inv_freq = torch.from_numpy(np.concatenate([inv, [0.0]]).astype(np.float32)).to(rt.device)
+
+    def kernel_libraries(self):
+        return tuple(set(ops.linear_libraries(self.fused.dtype, self.rt.dtype)) | {"core", hybrid.LIBRARY})
+
+    def cache_needs(self):
+        return [PagedRows(self.r + self.dr, self.window)]
+
+    def attention_flops(self, n_tokens: int) -> int:
+        pairs = n_tokens * (n_tokens + 1) // 2
+        if self.window and n_tokens > self.window:
+            pairs -= (n_tokens - self.window) * (n_tokens - self.window + 1) // 2
+        return 2 * self.heads * (2 * self.r + self.dr) * pairs
+
+    def run(self, rn: Runner, h, out, caches):
+        view = caches[0]
+        if not view.writable:
+            raise RuntimeError("latent attention writes the cache it reads")
+        H, dn, dr, dv, r = self.heads, self.dn, self.dr, self.dv, self.r
+        F, Dk = self.fused.shape[0], r + dr
+        fused = rn.buffer("la_fused", F, torch.float32)
+        rn.linear(h, self.fused, None, fused)
+        qp = rn.buffer("la_query", H * Dk, torch.float32)
+        table, bt_stride = rn.table(view)
+        pages = view.pages
+        rn.op("latent_prep", [fused.data_ptr(), fused.stride(0), self.dkv_col, keep(rn, self.latent_gain),
+                              keep(rn, self.inv_freq), self.rot_dims, rn.tok_req, rn.tok_pos, table, bt_stride,
+                              pages.shape[1], keep(rn, pages), pages.shape[0], ops.dtype_code(pages.dtype), rn.N, H,
+                              dn, dr, r, qp.data_ptr()], [self.eps])
+        rn.op("head_linear", [fused.data_ptr(), fused.stride(0), dn + dr, keep(rn, self.uk_t),
+                              ops.dtype_code(self.uk_t.dtype), qp.data_ptr(), ops.F32, qp.stride(0), Dk, rn.N, H, r, dn],
+              label="head_linear:absorb")
+        lat = rn.buffer("la_latent_out", H * r, torch.float32)
+        rn.op("latent_attention", [qp.data_ptr(), pages.data_ptr(), ops.dtype_code(pages.dtype), table, bt_stride,
+                                   pages.shape[1], pages.shape[0], rn.tok_req, rn.tok_pos,
+                                   fused.data_ptr() + 4 * self.gate_col, fused.stride(0), lat.data_ptr(), lat.stride(0),
+                                   rn.N, H, r, dr, self.window or 0], [self.scale])
+        o = rn.buffer("la_heads_out", H * dv)
+        rn.op("head_linear", [lat.data_ptr(), lat.stride(0), r, keep(rn, self.uv), ops.dtype_code(self.uv.dtype),
+                              o.data_ptr(), ops.dtype_code(o.dtype), o.stride(0), dv, rn.N, H, dv, r],
+              label="head_linear:values")
+        rn.linear(o, self.o, None, out)
+
+
+register_part("mixer", "latent_attention", LatentAttention)

@@ -101,6 +101,9 @@ def build_model(plan: ModelPlan, source, dtype: torch.dtype, device) -> CausalLM
         block_cls = part_class("block", layer.block)
         given = tuple((role, category) for role, category, _ in layer.parts)
         wanted = tuple(getattr(block_cls, "ROLES", ()))
+        optional = set(getattr(block_cls, "OPTIONAL_ROLES", ()))
+        if optional:                     # the roles the layer has, in the arrangement's order, none of the others missing
+            wanted = tuple(rc for rc in wanted if rc[0] not in optional or rc in given)
         if wanted and given != wanted:
             raise ValueError(f"layer {i}: the '{layer.block}' arrangement is made of {list(wanted)}; "
                              f"the plan gives {list(given)}")

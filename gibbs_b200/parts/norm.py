@@ -1,11 +1,18 @@
-"""RMSNorm: x * (1/sqrt(mean(x^2) + eps)) * gain, statistics in 32-bit
-(MisterTK/gibbs arch/lib/transformer.json5:9-11; src/model/simd.rs:73-111)."""
+"""Norms over rows of the residual stream.
+
+RMSNorm: x * (1/sqrt(mean(x^2) + eps)) * gain, statistics in 32-bit
+(MisterTK/gibbs arch/lib/transformer.json5:9-11; src/model/simd.rs:73-111), with the
+split-K and decode-product couplings of the core kernels.  RowNorm and its kinds (layer
+norm, plain RMS norm): the same statistics on the hybrid library, usable in front of a
+sublayer and behind one."""
 from __future__ import annotations
 
 import torch
 
 from .. import ops
+from ..ops import hybrid
 from .base import Norm, Residual, TensorDecl, VECTOR, register_part
+from .runner import Planned, Runner, keep, stream_tensor
 
 
 class RMSNorm(Norm):
@@ -43,3 +50,62 @@ class RMSNorm(Norm):
 
 
 register_part("norm", "rmsnorm", RMSNorm)
+
+
+class RowNorm(Norm):
+    """A norm over rows of the 32-bit stream with a gain and no bias, statistics in 32-bit,
+    on the hybrid library's kernels.  ``KIND`` picks the rule.  Besides the norm in front of
+    a sublayer (``forward``) it serves as the norm BEHIND one: ``add_normed`` adds
+    norm(y) * gain into the stream."""
+    KIND = hybrid.NORM_LAYER
+
+    @classmethod
+    def declare(cls, params):
+        return {"weight": TensorDecl.of(params["dim"], role=VECTOR)}
+
+    def __init__(self, params, tensors, rt):
+        super().__init__(params, tensors, rt)
+        self.dim, self.eps = int(params["dim"]), float(params["eps"])
+        self.gain = tensors["weight"].to(torch.float32).contiguous()
+
+    def kernel_libraries(self):
+        return ("core", hybrid.LIBRARY)
+
+    def run(self, rn: Runner, x: torch.Tensor, wanted_rows: bool = False) -> torch.Tensor:
+        out = rn.buffer("normed_wanted" if wanted_rows else "normed", self.dim)
+        rn.op("row_norm", [x.data_ptr(), x.stride(0), keep(rn, self.gain), out.data_ptr(), ops.dtype_code(out.dtype),
+                           rn.want_rows if wanted_rows else 0, rn.W if wanted_rows else rn.N, self.dim, self.KIND],
+              [self.eps], label="row_norm")
+        return out
+
+    def add_normed(self, rn: Runner, x: torch.Tensor, y: torch.Tensor) -> None:
+        """x += norm(y) * gain, for x the stream and y a sublayer's output (both float32)."""
+        rn.op("norm_add", [x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), keep(rn, self.gain), rn.N, self.dim,
+                           self.KIND], [self.eps], label="norm_add")
+
+    def forward(self, x, out=None, rows=None):
+        x = stream_tensor(x)
+        n = x.shape[0] if rows is None else rows.numel()
+        if out is None:
+            out = self.rt.empty(n, self.dim)
+        hybrid.call("row_norm", [x.data_ptr(), x.stride(0), self.gain.data_ptr(), out.data_ptr(),
+                                 ops.dtype_code(out.dtype), 0 if rows is None else rows.data_ptr(), n, self.dim,
+                                 self.KIND], [self.eps], device=self.rt.device)
+        return out
+
+    def plan_ops(self, plan, wanted_rows: bool = False, lazy: bool = False):
+        return self.run(Planned(plan), plan.residual, wanted_rows)
+
+
+class LayerNorm(RowNorm):
+    """(x - mean) / sqrt(var + eps) * gain, var the mean of the squared deviations."""
+    KIND = hybrid.NORM_LAYER
+
+
+class PlainRMSNorm(RowNorm):
+    """x / sqrt(mean(x^2) + eps) * gain."""
+    KIND = hybrid.NORM_RMS
+
+
+register_part("norm", "layernorm", LayerNorm)
+register_part("norm", "rmsnorm_rows", PlainRMSNorm)

@@ -28,7 +28,8 @@ def _seed_for(seed: int, name: str) -> int:
 
 
 def _is_gain(name: str) -> bool:
-    return name.endswith("norm.weight")
+    """A norm's gain: '...norm.weight', or a name whose last component names a norm ('l0.norm1b', 'final.norm')."""
+    return name.endswith("norm.weight") or "norm" in name.rsplit(".", 1)[-1]
 
 
 def random_tensors(plan: ModelPlan, seed: int, dtype: torch.dtype = torch.float32, std: float = 0.02,
