@@ -81,6 +81,9 @@ class ModelPlan:
     order: tuple[OrderEntry, ...]
     final_norm: PartSpec
     head: PartSpec
+    # checkpoint tensors that may be present although no part reads them (a layer without a
+    # feed-forward whose checkpoint still carries that sublayer's norms, say): fnmatch patterns
+    ignorable: tuple[str, ...] = ()
 
     def validate(self) -> None:
         for i, e in enumerate(self.order):

@@ -136,9 +136,13 @@ class PotivikConfig:
         def norm(tensor):
             return PartSpec("layernorm", {"dim": d, "eps": eps}, {"weight": tensor})
 
-        layers = []
+        layers, ignorable = [], []
+        if not side:
+            ignorable += ["side.embed", "l*.side.*"]
         for i, layer in enumerate(c["layers"]):
             p, m = f"l{i}", layer["mixer"]
+            if layer.get("mlp") is None:
+                ignorable += [f"{p}.norm2", f"{p}.norm2b"]
             if layer["type"] == "latent_attention":
                 mask, rot = m.get("mask") or {}, m["rot"]
                 mixer = PartSpec("latent_attention", {
@@ -190,6 +194,7 @@ class PotivikConfig:
             final_norm=norm("final.norm"),
             head=PartSpec("lm_head", {"vocab": vocab, "dim": d, "softcap": float(c.get("logit_softcap") or 0.0)},
                           {"weight": "head"}),
+            ignorable=tuple(ignorable),
         )
         plan.validate()
         return plan

@@ -235,8 +235,11 @@ GB_OP(gb_op_latent_attention) {
   const dim3 grid(n, gb_div_up(H, LA_HB)), block(32 * LA_HB);
 #define LA(TC, RL)                                                                                                   \
   do {                                                                                                               \
-    if (smem > 48 * 1024)                                                                                            \
+    static size_t allowed = 48 * 1024;     /* raised once per size, before any stream capture replays the launch */ \
+    if (smem > allowed) {                                                                                            \
       GB_CUDA(cudaFuncSetAttribute(latent_attention_kernel<TC, RL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+      allowed = smem;                                                                                                \
+    }                                                                                                                \
     gb_launch(latent_attention_kernel<TC, RL>, grid, block, smem, ctx->stream, op_ptr<const float>(a[0]),             \
               op_ptr<const TC>(a[1]), op_ptr<const int>(a[3]), (int)a[4], (int)a[5], (int)a[6], op_ptr<const int>(a[7]), \
               op_ptr<const int>(a[8]), op_ptr<const float>(a[9]), a[10], op_ptr<float>(a[11]), a[12], H, r, dr,       \

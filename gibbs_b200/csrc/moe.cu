@@ -170,14 +170,14 @@ __global__ void moe_combine_kernel(const float* out, long long ldo, const int* p
 
 }  // namespace
 
-// a0 logits (f32), a1 their row stride, a2 tokens, a3 experts, a4 top, a5 column of the shared expert's gate logit or
-// -1, a6 chosen experts [tokens, top] (int32), a7 their weights (f32), a8 shared gate [tokens] (f32) or 0
+// a0 logits (f32), a1 their row stride, a2 tokens, a3 experts, a4 top, a5 column of the shared expert's gate logit,
+// a6 chosen experts [tokens, top] (int32), a7 their weights (f32), a8 shared gate [tokens] (f32), or 0 for none
 GB_OP(gb_op_moe_route) {
   const int n = (int)a[2], E = (int)a[3], top = (int)a[4];
   if (n <= 0) return 0;
   if (top < 1 || top > E) GB_FAIL(GB_ERR_ARG, "moe_route: top %d of %d experts", top, E);
   gb_launch(moe_route_kernel, dim3(gb_div_up(n, 128)), dim3(128), 0, ctx->stream, op_ptr<const float>(a[0]), a[1], n, E,
-            top, (int)a[5], op_ptr<int>(a[6]), op_ptr<float>(a[7]), a[5] >= 0 ? op_ptr<float>(a[8]) : nullptr);
+            top, (int)a[5], op_ptr<int>(a[6]), op_ptr<float>(a[7]), op_ptr<float>(a[8]));
   GB_CHECK_LAUNCH("moe_route");
   return 1;
 }

@@ -36,6 +36,8 @@ def pages_for(model: CausalLM, page_size: int, max_running: int, ctx: int, memor
                 if hasattr(need, "kv_heads"):
                     per_token += need.kv_heads * (need.head_dim + need.value_dim) \
                         * (2 if model.rt.dtype == torch.bfloat16 else 4)
+                elif hasattr(need, "width"):             # one plain row per position (PagedRows)
+                    per_token += need.width * (2 if model.rt.dtype == torch.bfloat16 else 4)
     want = max_running * -(-ctx // page_size)
     if per_token == 0:
         return 1

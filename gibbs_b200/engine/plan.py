@@ -135,6 +135,9 @@ class PlanBuilder:
         self._lazy = None
         if len(a) > 23:
             raise NotPlannable("an operation has 23 integer operands")
+        if any(int(v) < 0 for v in a):
+            # (bit 62 marks a symbol, and every negative number has it set)
+            raise ValueError(f"operation {label or op}: operands are non-negative numbers, addresses or symbols; got {list(a)}")
         label = label or f"op{op}"
         if label not in self.labels:
             self.labels.append(label)

@@ -50,6 +50,8 @@ def call(name: str, a, f=(), flags: int = 0, device=None) -> int:
     fn = _function(name)
     if len(a) > 24 or len(f) > 3:
         raise ValueError("an operation has 24 integer and 3 floating-point operands")
+    if any(int(v) < 0 for v in a):
+        raise ValueError(f"{name}: operands are non-negative numbers or addresses (a plan keeps bit 62 for symbols); got {list(a)}")
     ia = (ctypes.c_longlong * 24)(*[int(v) for v in a])
     fa = (ctypes.c_double * 3)(*[float(v) for v in f])
     status = device_status(device if device is not None else torch.device("cuda", torch.cuda.current_device()))

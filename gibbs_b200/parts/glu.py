@@ -107,8 +107,8 @@ class RoutedGLU(BranchPart, FeedForward):
         idx = rn.buffer("moe_choice", top, torch.int32)
         wts = rn.buffer("moe_weight", top, torch.float32)
         sg = rn.buffer("moe_shared_gate", 1, torch.float32)
-        rn.op("moe_route", [logits.data_ptr(), logits.stride(0), rn.N, E, top, E if shared else -1, idx.data_ptr(),
-                            wts.data_ptr(), sg.data_ptr()])
+        rn.op("moe_route", [logits.data_ptr(), logits.stride(0), rn.N, E, top, E, idx.data_ptr(), wts.data_ptr(),
+                            sg.data_ptr() if shared else 0])
         offsets = rn.buffer("moe_offsets", E + 1, torch.int32, fixed_rows=1)
         row_pair = rn.buffer("moe_row_pair", top, torch.int32)
         pair_row = rn.buffer("moe_pair_row", top, torch.int32)

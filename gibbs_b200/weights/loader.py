@@ -13,6 +13,7 @@ which makes the 32-bit run of a bfloat16 checkpoint its exact twin.
 """
 from __future__ import annotations
 
+import fnmatch
 from collections import Counter
 
 import torch
@@ -73,7 +74,8 @@ class WeightBinder:
     def verify(self) -> None:
         have = set(self.source.names())
         missing = [(n, d.shapes[0]) for n, d in self.decls.items() if n not in have]
-        unexpected = [(n, self.source.shape(n)) for n in sorted(have - set(self.decls))]
+        unexpected = [(n, self.source.shape(n)) for n in sorted(have - set(self.decls))
+                      if not any(fnmatch.fnmatchcase(n, pat) for pat in getattr(self.plan, "ignorable", ()))]
         wrong = [(n, d.shapes, self.source.shape(n)) for n, d in self.decls.items()
                  if n in have and tuple(self.source.shape(n)) not in d.shapes]
         wrong += [(n, shapes, got) for n, shapes, got in self._conflicts]

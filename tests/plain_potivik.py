@@ -57,7 +57,8 @@ def latent_attention(h, m, W, eps):
     window - 1 positions before it."""
     T = h.shape[0]
     H, dn, dr, dv, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
-    base, rdims, window, scale = m["rot"]["base"], m["rot"]["dims"], m["mask"]["size"], m["scale"]
+    base, rdims, scale = m["rot"]["base"], m["rot"].get("dims", dr), m["scale"]
+    window = (m.get("mask") or {}).get("size") or T              # no mask: every earlier position
     pos = torch.arange(T)
     q = (h @ W["q"].T).reshape(T, H, dn + dr)
     q_plain, q_rot = q[..., :dn], rotate_pairs(q[..., dn:], pos, base, rdims)

@@ -1,0 +1,217 @@
+"""Shared by the Potivik tests: two small configurations that differ in every
+size and option, weights with realistic scales (all values exactly
+representable in bfloat16, so that both compute dtypes and the plain
+implementation read the same numbers), model folders, and a harness that runs
+ONE mixer alone over a request cut into portions."""
+from __future__ import annotations
+
+import json
+import math
+from pathlib import Path
+
+import numpy as np
+import torch
+
+# layers: latent attention with a window and a partly rotated part + routed experts (top 2, shared expert);
+# state-space mixer with two groups and two norm groups + dense unit; a layer without a feed-forward; latent
+# attention without a window + routed experts (top 3, no shared expert).  Per-token input and a soft cap.
+CFG_A = {
+    "architecture": "Potivik", "vocab": 300, "width": 64, "norm": {"eps": 1e-5}, "logit_softcap": 10.0,
+    "token_side": {"dim": 8},
+    "layers": [
+        {"type": "latent_attention",
+         "mixer": {"heads": 3, "dim": 16, "rot_dim": 8, "vdim": 24, "kv_rank": 40, "scale": 0.35,
+                   "mask": {"size": 19}, "rot": {"base": 1000.0, "dims": 4}},
+         "mlp": {"kind": "moe", "router": {"experts": 6, "top": 2}, "expert": {"ff": 40, "limit": 1.5},
+                 "shared": {"ff": 24, "limit": 3.0}}},
+        {"type": "mamba2",
+         "mixer": {"heads": 4, "vdim": 12, "state": 20, "groups": 2, "conv": 4, "norm_groups": 2},
+         "mlp": {"kind": "dense", "ff": 72, "limit": 0.8}},
+        {"type": "mamba2",
+         "mixer": {"heads": 4, "vdim": 12, "state": 20, "groups": 2, "conv": 4, "norm_groups": 2},
+         "mlp": None},
+        {"type": "latent_attention",
+         "mixer": {"heads": 3, "dim": 16, "rot_dim": 8, "vdim": 24, "kv_rank": 40, "scale": 0.35,
+                   "rot": {"base": 1000.0, "dims": 8}},
+         "mlp": {"kind": "moe", "router": {"experts": 5, "top": 3}, "expert": {"ff": 16, "limit": 2.0}}},
+    ],
+}
+# more than eight heads, a latent wider than 64, a state wider than 64 that is no multiple of 32, a convolution
+# of two taps, one expert per token, no per-token input, no soft cap
+CFG_B = {
+    "architecture": "Potivik", "vocab": 257, "width": 96, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "mamba2",
+         "mixer": {"heads": 2, "vdim": 40, "state": 70, "groups": 1, "conv": 2, "norm_groups": 1},
+         "mlp": {"kind": "moe", "router": {"experts": 3, "top": 1}, "expert": {"ff": 48, "limit": 2.5},
+                 "shared": {"ff": 32, "limit": 2.5}}},
+        {"type": "latent_attention",
+         "mixer": {"heads": 10, "dim": 8, "rot_dim": 16, "vdim": 8, "kv_rank": 72, "scale": 0.3,
+                   "mask": {"size": 33}, "rot": {"base": 50000.0, "dims": 16}},
+         "mlp": {"kind": "dense", "ff": 128, "limit": 1.0}},
+    ],
+}
+CONFIGS = {"A": (CFG_A, 11), "B": (CFG_B, 12)}
+
+
+def _bf16_exact(t: torch.Tensor) -> torch.Tensor:
+    return t.to(torch.bfloat16).to(torch.float32)
+
+
+def make_weights(cfg: dict, seed: int) -> dict:
+    """name -> float32 tensor (bfloat16-exact values) for every tensor of the design."""
+    g = torch.Generator().manual_seed(seed)
+    d, V = cfg["width"], cfg["vocab"]
+    W = {}
+
+    def mat(name, out, inp, scale=1.0):
+        W[name] = torch.randn(out, inp, generator=g) * (scale / math.sqrt(inp))
+
+    def gain(name, n):
+        W[name] = 1.0 + 0.15 * torch.randn(n, generator=g)
+
+    W["embed"] = torch.randn(V, d, generator=g)
+    side = cfg.get("token_side")
+    if side:
+        W["side.embed"] = torch.randn(V, len(cfg["layers"]) * side["dim"], generator=g)
+    for i, layer in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        gain(p + "norm1", d), gain(p + "norm1b", d)
+        if layer["type"] == "latent_attention":
+            H, dn, dr, dv, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            mat(p + "mix.q", H * (dn + dr), d, 1.6), mat(p + "mix.dkv", r + dr, d, 1.6)
+            gain(p + "mix.dkv.norm", r)
+            mat(p + "mix.uk", H * dn, r, 1.3), mat(p + "mix.uv", H * dv, r), mat(p + "mix.g", H, d, 2.0)
+            mat(p + "mix.o", d, H * dv)
+        else:
+            H, P, N, G, K = m["heads"], m["vdim"], m["state"], m["groups"], m["conv"]
+            inner, ch = H * P, H * P + 2 * G * N
+            mat(p + "mix.in", 2 * inner + 2 * G * N + H, d)
+            W[p + "mix.conv"] = torch.randn(ch, K, generator=g) * 0.5
+            W[p + "mix.conv.b"] = torch.randn(ch, generator=g) * 0.1
+            W[p + "mix.dt_bias"] = torch.randn(H, generator=g) * 0.7 - 1.5
+            W[p + "mix.A_log"] = torch.log(0.3 + 3.0 * torch.rand(H, generator=g))
+            W[p + "mix.D"] = 1.0 + 0.2 * torch.randn(H, generator=g)
+            gain(p + "mix.norm", inner)
+            mat(p + "mix.o", d, inner)
+        f = layer.get("mlp")
+        if f is not None:
+            gain(p + "norm2", d), gain(p + "norm2b", d)
+            if f["kind"] == "dense":
+                mat(p + "mlp.gate", f["ff"], d, 1.5), mat(p + "mlp.up", f["ff"], d, 1.5), mat(p + "mlp.down", d, f["ff"])
+            else:
+                E, ff = f["router"]["experts"], f["expert"]["ff"]
+                mat(p + "mlp.router", E, d, 2.0)
+                for e in range(E):
+                    mat(p + f"mlp.e{e}.gate", ff, d, 1.5), mat(p + f"mlp.e{e}.up", ff, d, 1.5), mat(p + f"mlp.e{e}.down", d, ff)
+                if f.get("shared"):
+                    sf = f["shared"]["ff"]
+                    mat(p + "mlp.shared.gate", sf, d, 1.5), mat(p + "mlp.shared.up", sf, d, 1.5)
+                    mat(p + "mlp.shared.down", d, sf), mat(p + "mlp.shared.sg", 1, d, 1.5)
+        if side:
+            mat(p + "side.gate", side["dim"], d), mat(p + "side.proj", d, side["dim"]), gain(p + "side.norm", d)
+    gain("final.norm", d)
+    mat("head", V, d, 3.0)
+    return {k: _bf16_exact(v) for k, v in W.items()}
+
+
+def write_model(folder, cfg: dict, W: dict, stored=torch.bfloat16) -> Path:
+    from gibbs_b200.weights.safetensors_io import write_safetensors
+    folder = Path(folder)
+    folder.mkdir(parents=True, exist_ok=True)
+    (folder / "config.json").write_text(json.dumps(cfg, indent=1))
+    write_safetensors(folder / "model.safetensors", ((k, v.to(stored)) for k, v in W.items()), metadata={"format": "pt"})
+    return folder
+
+
+def build(name: str, dtype: str, device="cuda:0"):
+    """(config dict, weights, model on the device) of a named configuration."""
+    from gibbs_b200.config import parse_config
+    from gibbs_b200.engine.loading import parse_dtype
+    from gibbs_b200.parts.model import build_model
+    from gibbs_b200.weights import TensorDict
+    cfg, seed = CONFIGS[name]
+    W = make_weights(cfg, seed)
+    conf = parse_config(cfg)
+    model = build_model(conf.plan(), TensorDict({k: v.to(torch.bfloat16) for k, v in W.items()}), parse_dtype(dtype), device)
+    model.config = conf
+    return cfg, W, model
+
+
+def ids_for(cfg: dict, seed: int, n: int) -> list:
+    rng = np.random.default_rng(seed)
+    return [int(v) for v in rng.integers(0, cfg["vocab"], n)]
+
+
+class PartHarness:
+    """Runs one mixer alone, with a cache manager and step builder of its own, over a request cut
+    into portions.  ``feed(request, h)`` runs the next tokens of a request and returns the mixer's
+    output for them (float32)."""
+
+    def __init__(self, part, n_pages=64, page_size=16, n_slots=3, max_context=1024, guard=True):
+        from gibbs_b200.cache import CacheManager
+        from gibbs_b200.engine.step import StepBuilder
+        self.part, self.rt = part, part.rt
+        self.cache = CacheManager([(getattr(part, 'cache_needs', list)(), None)], n_pages, page_size, n_slots, part.rt.dtype, part.rt.device,
+                                  max_context, guard=guard)
+        self.builder = StepBuilder(self.cache, part.rt.device, n_slots, max_context)
+
+    def feed_many(self, portions: dict) -> dict:
+        """portions: {request: h [n, hidden] float32 on the CPU}; one step for all of them."""
+        from gibbs_b200.engine.step import StepEntry
+        rcs, entries = [], []
+        for rid, h in portions.items():
+            if rid not in self.cache.live:
+                self.cache.open(rid)
+            rc = self.cache.live[rid]
+            rcs.append(rc)
+            entries.append(StepEntry(rid, [0] * h.shape[0], []))
+        self.cache.reserve_all([(rc, rc.length + len(e.tokens)) for rc, e in zip(rcs, entries)])
+        step, caches = self.builder.build(entries, rcs)
+        h = torch.cat(list(portions.values()), 0).to(self.rt.device, self.rt.dtype).contiguous()
+        out = torch.full((h.shape[0], self.part.hidden), float("nan"), dtype=torch.float32, device=self.rt.device)
+        self.part.forward(h, out, step, caches[0])
+        torch.cuda.synchronize()
+        for rc, e in zip(rcs, entries):
+            self.cache.advance(rc, rc.length + len(e.tokens))
+        self.cache.check()
+        res, at = {}, 0
+        for rid, hh in portions.items():
+            res[rid] = out[at:at + hh.shape[0]].cpu()
+            at += hh.shape[0]
+        return res
+
+    def feed(self, rid, h):
+        return self.feed_many({rid: h})[rid]
+
+    def close(self, rid):
+        self.cache.close(rid)
+
+    def run_cut(self, rid, h, cuts):
+        """The whole of h for one request, in portions of the given sizes (the last size repeats)."""
+        outs, at, k = [], 0, 0
+        while at < h.shape[0]:
+            n = min(cuts[min(k, len(cuts) - 1)], h.shape[0] - at)
+            outs.append(self.feed(rid, h[at:at + n]))
+            at, k = at + n, k + 1
+        return torch.cat(outs, 0)
+
+
+def make_part(category: str, kind: str, params: dict, tensors: dict, dtype=torch.float32, device="cuda:0"):
+    """A part built directly from tensors (float32, bfloat16-exact), as the loader would hand them over."""
+    from gibbs_b200.parts.base import MATRIX, Runtime, part_class
+    cls = part_class(category, kind)
+    rt = Runtime(dtype=dtype, device=torch.device(device))
+    decl = cls.declare(params)
+    given = {}
+    for name, d in decl.items():
+        t = tensors[name].reshape(d.shapes[0])
+        mem = dtype if (d.role == MATRIX and dtype == torch.bfloat16) else torch.float32
+        given[name] = t.to(device=device, dtype=mem).contiguous()
+    return cls(params, given, rt)
+
+
+def rel_rows(got, want) -> np.ndarray:
+    """Per-row relative L2 error."""
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    return np.linalg.norm(got - want, axis=-1) / (np.linalg.norm(want, axis=-1) + 1e-30)

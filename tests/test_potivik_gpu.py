@@ -1,0 +1,420 @@
+"""The Potivik design on the GPU against the plain implementation
+(tests/plain_potivik.py): every mechanism alone, then whole models through the
+engine's step function, cut and batched in every way, then greedy generation
+through the scheduler.
+
+Where both compute dtypes run: float32 must match every row; in bfloat16 a
+router choice at a near tie may flip under the rounding of the router's
+input, which changes that token's row (and, faintly, later ones), so whole
+models with routed experts are held to "nearly all rows" there.  Mechanisms
+alone have no such ties and are held to every row in both.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_potivik as plain
+from helpers import run_trace_on_engine, trace_mixed, trace_portions, trace_tail_decoded, trace_whole
+from potivik_helpers import CFG_A, CFG_B, CONFIGS, PartHarness, build, ids_for, make_part, make_weights, rel_rows
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 2e-4, "bfloat16": 4e-2}
+DEV = "cuda:0"
+
+
+def gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def bf(t):
+    return t.to(torch.bfloat16).to(torch.float32)
+
+
+def check_rows(got, want, dtype: str, strict: bool = True, what: str = ""):
+    e = rel_rows(got, want)
+    if strict or dtype == "float32":
+        assert e.max() <= TOL[dtype], f"{what}: row {int(e.argmax())} differs by {e.max():.3g} (tolerance {TOL[dtype]})"
+    else:
+        # (measured: a flipped choice shows in up to a third of a short request's rows; the median stays at 1.4e-2)
+        frac = float((e > TOL[dtype]).mean())
+        assert frac <= 0.45 and np.median(e) <= TOL[dtype] / 2, \
+            f"{what}: {frac:.1%} of the rows differ by more than {TOL[dtype]} (median {np.median(e):.3g})"
+
+
+# ---------------------------------------------------------------------------
+# mechanisms alone
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kind,ref", [("layernorm", plain.layer_norm), ("rmsnorm_rows", plain.rms_norm)])
+def test_norm_in_front_and_behind(kind, ref, dtype):
+    g = gen(1)
+    dim = 200
+    x = torch.randn(37, dim, generator=g) * 3 + 1.5          # a mean far from zero: the variance is of deviations
+    y = torch.randn(37, dim, generator=g) * 0.01 + 4.0
+    w = 1 + 0.2 * torch.randn(dim, generator=g)
+    part = make_part("norm", kind, {"dim": dim, "eps": 1e-5}, {"weight": w}, DTYPES[dtype])
+    xd = x.to(DEV)
+    out = part.forward(xd).float().cpu()
+    check_rows(out, ref(x.double(), w.double(), 1e-5), dtype, what="norm")
+    rows = torch.tensor([5, 0, 36, 5], dtype=torch.int32, device=DEV)
+    out = part.forward(xd, rows=rows).float().cpu()
+    check_rows(out, ref(x.double(), w.double(), 1e-5)[[5, 0, 36, 5]], dtype, what="gathered rows")
+    # behind a sublayer: x += norm(y) * w, always in 32-bit
+    from gibbs_b200.engine.step import StepState
+    from gibbs_b200.parts.runner import Eager
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    step = StepState(37, 1, 0, z, z, z, z, z, z, z, z, z)
+    part.add_normed(Eager(part.rt, step), xd, y.to(DEV))
+    want = x.double() + ref(y.double(), w.double(), 1e-5)
+    assert rel_rows(xd.cpu(), want).max() < 2e-5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_clamped_unit_alone(dtype):
+    g = gen(2)
+    d, f, limit = 64, 40, 0.7
+    W = {k: bf(torch.randn(*s, generator=g) * 0.3) for k, s in (("gate", (f, d)), ("up", (f, d)), ("down", (d, f)))}
+    part = make_part("feed_forward", "clamped_glu", {"hidden": d, "inner": f, "limit": limit}, W, DTYPES[dtype])
+    h = bf(torch.randn(50, d, generator=g) * 2)               # many pre-activations beyond the clamps, on both sides
+    hz = PartHarness(part)
+    got = hz.feed("a", h)
+    want = plain.clamped_glu(h.double(), W["gate"].double(), W["up"].double(), W["down"].double(), limit)
+    check_rows(got, want, dtype, what="clamped unit")
+    assert (h @ W["gate"].T > limit).any() and (h @ W["up"].T < -limit).any()
+
+
+def _attention_params(m, d):
+    return {"hidden": d, "heads": m["heads"], "dim": m["dim"], "rot_dim": m["rot_dim"], "vdim": m["vdim"],
+            "kv_rank": m["kv_rank"], "scale": m["scale"], "window": (m.get("mask") or {}).get("size"),
+            "rot_base": m["rot"]["base"], "rot_dims": m["rot"].get("dims", m["rot_dim"]), "eps": 1e-5}
+
+
+def _mixer_weights(cfg, layer, seed):
+    W = make_weights(cfg, seed)
+    return plain.sub(W, f"l{layer}.mix.")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cfg,layer", [(CFG_A, 0), (CFG_A, 3), (CFG_B, 1)])
+def test_latent_attention_alone_whole_cut_and_decoded(cfg, layer, dtype):
+    m, d = cfg["layers"][layer]["mixer"], cfg["width"]
+    W = _mixer_weights(cfg, layer, 5)
+    part = make_part("mixer", "latent_attention", _attention_params(m, d), W, DTYPES[dtype])
+    T = 150
+    h = bf(torch.randn(T, d, generator=gen(6)))
+    want = plain.latent_attention(h.double(), m, {k: v.double() for k, v in W.items()}, 1e-5)
+    hz = PartHarness(part, n_pages=12, page_size=16)          # 12 pages: 192 positions, pages come back and go out again
+    for rid, cuts in (("whole", [T]), ("cut", [2, 3, 17, 2, 31, 16, 1, 5, 64, 7]), ("decoded", [T - 45, 1])):
+        got = hz.run_cut(rid, h, cuts)
+        check_rows(got, want, dtype, what=f"latent attention, {rid}")
+        hz.close(rid)
+
+
+def _pointed_attention(window, T, hot_key, query, d=64, seed=7):
+    """Weights and inputs for which the query position's score against ``hot_key`` stands far
+    above all others (when that key is visible), and whose values tell keys apart.  The latent is
+    the input's first entries, the unrotated key of head 0 is the latent's first entries, the
+    query is the input scaled: q . k_j = gamma * h_q . rmsnorm(h_j)."""
+    H, dn, dr, dv, r = 2, 16, 4, 8, 24
+    m = {"heads": H, "dim": dn, "rot_dim": dr, "vdim": dv, "kv_rank": r, "scale": 1.0, "rot": {"base": 100.0, "dims": dr}}
+    if window:
+        m["mask"] = {"size": window}
+    g = gen(seed)
+    W = {"q": torch.zeros(H * (dn + dr), d), "dkv": torch.zeros(r + dr, d), "dkv.norm": torch.ones(r),
+         "uk": torch.zeros(H * dn, r), "uv": bf(torch.randn(H * dv, r, generator=g)), "g": torch.zeros(H, d),
+         "o": bf(torch.randn(d, H * dv, generator=g) / 4)}
+    for i in range(r):
+        W["dkv"][i, i] = 1.0
+    for hh in range(H):
+        for i in range(dn):
+            W["uk"][hh * dn + i, i] = 1.0
+            W["q"][hh * (dn + dr) + i, i] = 1.0
+    h = bf(torch.randn(T, d, generator=g))
+    h[:, r:] = 0
+    key = h[hot_key, :dn] / h[hot_key, :r].pow(2).mean().sqrt()
+    h[query] = 0
+    h[query, :dn] = bf(6.0 * key / key.norm())               # score against the hot key: about 6 |k|, others a few units
+    h[query, dn:r] = 30.0                                     # (a long latent: the query's own key scores low)
+    return m, W, h
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("decoded", [False, True])
+@pytest.mark.parametrize("window,T,hot,query", [
+    (40, 120, 60, 99),        # the oldest key the window keeps (99 - 60 = 39)
+    (40, 120, 59, 99),        # the first one it has dropped
+    (40, 120, 0, 39),         # the first token of the sequence, just inside
+    (40, 120, 0, 40),         # ... and just outside
+    (16, 120, 80, 95),        # a window of one page: its edge is a page's edge
+    (16, 120, 79, 95),
+    (None, 400, 3, 399),      # no window: a key hundreds of positions back
+    (None, 400, 16, 399),     # ... at a page's first row
+    (300, 400, 100, 399),     # a long window: far but inside
+    (300, 400, 99, 399),      # ... and outside
+])
+def test_latent_attention_finds_the_one_key_that_matters(window, T, hot, query, decoded, dtype):
+    m, W, h = _pointed_attention(window, T, hot, query)
+    part = make_part("mixer", "latent_attention", _attention_params(m, h.shape[1]), W, DTYPES[dtype])
+    want = plain.latent_attention(h.double(), m, {k: v.double() for k, v in W.items()}, 1e-5)
+    visible = window is None or query - hot < window
+    hz = PartHarness(part, n_pages=32, page_size=16)
+    got = hz.run_cut("r", h, [query - 10, 1] if decoded else [T])
+    e = rel_rows(got, want)
+    assert e[query] <= TOL[dtype], f"query row differs by {e[query]:.3g}"
+    assert e.max() <= TOL[dtype]
+    # the hot key's value dominates the output exactly when it is visible
+    c_hot = plain.rms_norm(h[hot, :m["kv_rank"]].double(), None, 1e-5)
+    v_hot = (W["uv"].double() @ c_hot) * 0.5                   # gate logits are zero: sigmoid = 1/2
+    out_hot = W["o"].double() @ v_hot
+    close = float((got[query].double() - out_hot).norm() / out_hot.norm())
+    assert (close < 0.2) == visible, f"hot key visible={visible}, distance to its value {close:.3g}"
+
+
+def _ssm_params(m, d):
+    return {"hidden": d, "heads": m["heads"], "vdim": m["vdim"], "state": m["state"], "groups": m["groups"],
+            "conv": m["conv"], "norm_groups": m.get("norm_groups", 1), "eps": 1e-5}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cfg,layer", [(CFG_A, 1), (CFG_B, 0)])
+def test_state_space_mixer_alone_whole_cut_and_decoded(cfg, layer, dtype):
+    m, d = cfg["layers"][layer]["mixer"], cfg["width"]
+    W = _mixer_weights(cfg, layer, 8)
+    part = make_part("mixer", "state_space", _ssm_params(m, d), W, DTYPES[dtype])
+    T = 90
+    h = bf(torch.randn(T, d, generator=gen(9)))
+    want = plain.mamba2(h.double(), m, {k: v.double() for k, v in W.items()}, 1e-5)
+    hz = PartHarness(part, n_slots=2)
+    for rid, cuts in (("whole", [T]), ("cut", [2, 1, 3, 17, 2, 31, 1, 1, 5]), ("decoded", [T - 40, 1])):
+        got = hz.run_cut(rid, h, cuts)
+        check_rows(got, want, dtype, what=f"state-space mixer, {rid}")
+        hz.close(rid)                                           # the slot goes back and is taken again, zeroed
+
+
+def test_state_space_state_is_carried_far_and_a_reused_slot_starts_at_zero():
+    """Decay close to one and a strong first token: position 0 still shows 300 tokens later, however
+    the sequence is cut; and the next request in the same slot does not see it."""
+    cfg = {"heads": 2, "vdim": 8, "state": 16, "groups": 1, "conv": 3, "norm_groups": 1}
+    d = 32
+    W = _mixer_weights({**CFG_A, "width": d, "layers": [{"type": "mamba2", "mixer": cfg, "mlp": None}],
+                        "token_side": None}, 0, 10)
+    W["A_log"] = torch.full((2,), math.log(0.02))             # exp(-0.02 dt): almost no forgetting
+    part = make_part("mixer", "state_space", _ssm_params(cfg, d), W, torch.float32)
+    T = 300
+    h = bf(torch.randn(T, d, generator=gen(11)) * 0.3)
+    h2 = h.clone()
+    h2[0] = bf(h[0] * 8 + 1)
+    Wd = {k: v.double() for k, v in W.items()}
+    want, want2 = plain.mamba2(h.double(), cfg, Wd, 1e-5), plain.mamba2(h2.double(), cfg, Wd, 1e-5)
+    assert np.median(rel_rows(want[-20:], want2[-20:])) > 1e-3  # the first token matters at the end
+    hz = PartHarness(part, n_slots=1)
+    got2 = hz.run_cut("first", h2, [7, 2, 64, 1, 1, 100, 3])
+    assert rel_rows(got2, want2).max() <= TOL["float32"]
+    hz.close("first")
+    got = hz.run_cut("second", h, [150, 1])                    # same slot
+    assert rel_rows(got, want).max() <= TOL["float32"]
+
+
+def _routed_params(f, d):
+    sh = f.get("shared")
+    return {"hidden": d, "experts": f["router"]["experts"], "top": f["router"]["top"], "expert_inner": f["expert"]["ff"],
+            "expert_limit": f["expert"]["limit"], "shared_inner": sh["ff"] if sh else 0,
+            "shared_limit": sh["limit"] if sh else 0.0}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cfg,layer", [(CFG_A, 0), (CFG_A, 3), (CFG_B, 0)])
+def test_routed_experts_alone(cfg, layer, dtype):
+    f, d = cfg["layers"][layer]["mlp"], cfg["width"]
+    W = plain.sub(make_weights(cfg, 13), f"l{layer}.mlp.")
+    # router rows far apart, so that no choice hangs on the rounding of the input
+    E = f["router"]["experts"]
+    W["router"] = bf(torch.randn(E, d, generator=gen(14)) * 0.9)
+    part = make_part("feed_forward", "routed_glu", _routed_params(f, d), W, DTYPES[dtype])
+    T = 140                                                    # more than one tile of rows for some expert
+    h = bf(torch.randn(T, d, generator=gen(15)))
+    z = h.double() @ W["router"].double().T
+    top = f["router"]["top"]
+    srt = torch.sort(z, dim=1, descending=True).values
+    keep = (srt[:, top - 1] - srt[:, top]) > 0.15 if top < E else torch.ones(T, dtype=torch.bool)
+    h = h[keep]
+    want = plain.moe_ff(h.double(), f, {k: v.double() for k, v in W.items()})
+    hz = PartHarness(part)
+    got = hz.feed("a", h)
+    check_rows(got, want, dtype, what="routed experts")
+    # an expert's weight multiplies its INPUT: through the clamps that is not the same as scaling the output
+    s = torch.sigmoid(z[keep])
+    experts_only = plain.moe_ff(h.double(), {**f, "shared": None}, {k: v.double() for k, v in W.items()})
+    other = torch.zeros_like(want)
+    for t in range(h.shape[0]):
+        for e in torch.topk(s[t], top).indices.tolist():
+            other[t] += s[t, e] * plain.clamped_glu(h[t:t + 1].double(), W[f"e{e}.gate"].double(), W[f"e{e}.up"].double(),
+                                                    W[f"e{e}.down"].double(), f["expert"]["limit"])[0]
+    assert rel_rows(experts_only, other).max() > 0.05
+    # one token at a time gives the same rows as the batch
+    single = torch.cat([hz.feed("b", h[t:t + 1]) for t in range(6)], 0)
+    assert rel_rows(single, got[:6]).max() <= (1e-5 if dtype == "float32" else 2e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_token_input_alone(dtype):
+    g = gen(16)
+    d, dim, V, L = 48, 8, 50, 3
+    W = {"table": bf(torch.randn(V, L * dim, generator=g)), "gate": bf(torch.randn(dim, d, generator=g) / 7),
+         "proj": bf(torch.randn(d, dim, generator=g) / 3), "norm": 1 + 0.2 * torch.randn(d, generator=g)}
+    for layer in (0, 2):
+        part = make_part("token_input", "gated_token_input",
+                         {"hidden": d, "dim": dim, "offset": layer * dim, "table_width": L * dim, "vocab": V, "eps": 1e-5},
+                         W, DTYPES[dtype])
+        x = torch.randn(20, d, generator=g)
+        ids = torch.randint(0, V, (20,), generator=g)
+        from gibbs_b200.engine.step import StepState
+        z = torch.zeros(1, dtype=torch.int32, device=DEV)
+        step = StepState(20, 1, 0, ids.to(DEV, torch.int32), z, z, z, z, z, z, z, z)
+        xd = x.to(DEV)
+        part.forward(xd, step)
+        want = plain.token_side(x.double(), ids, W["table"].double(), layer * dim, (layer + 1) * dim,
+                                {k: W[k].double() for k in ("gate", "proj", "norm")}, 1e-5)
+        assert rel_rows(xd.cpu(), want).max() <= (1e-5 if dtype == "float32" else 2e-2)
+
+
+# ---------------------------------------------------------------------------
+# whole models through the engine
+# ---------------------------------------------------------------------------
+
+_CACHE: dict = {}
+
+
+def model_and_truth(name: str, dtype: str, lengths=(1, 2, 23, 61, 130)):
+    """A model, some requests, and the plain implementation's logits for them."""
+    key = (name, dtype)
+    if key not in _CACHE:
+        cfg, W, model = build(name, dtype)
+        reqs = {f"r{n}": ids_for(cfg, 100 + n, n) for n in lengths}
+        tkey = ("truth", name)
+        if tkey not in _CACHE:
+            _CACHE[tkey] = {rid: plain.forward(cfg, W, ids).numpy() for rid, ids in reqs.items()}
+        _CACHE[key] = (cfg, model, reqs, _CACHE[tkey])
+    return _CACHE[key]
+
+
+def engine_for(model, n_pages=64, page_size=16, max_requests=4, cap=512, **kw):
+    from gibbs_b200 import Engine
+    return Engine(model, n_pages=n_pages, page_size=page_size, max_requests=max_requests, max_step_tokens=cap,
+                  max_context=cap, guard_cache=True, **kw)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_whole_decoded_and_cut_prompts_match_the_plain_implementation(name, dtype):
+    cfg, model, reqs, truth = model_and_truth(name, dtype)
+    eng = engine_for(model)
+    assert eng.plan is not None, eng.plan_refusal
+    for what, steps in (("whole", trace_whole(reqs)), ("decoded", trace_tail_decoded(reqs, tail=40)),
+                        ("cut", trace_portions(reqs))):
+        got = run_trace_on_engine(eng, steps)
+        for rid in reqs:
+            check_rows(got[rid], truth[rid], dtype, strict=False, what=f"{name} {what} {rid}")
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_layer_by_layer_in_float32(name):
+    """The residual stream after every layer, through the parts' forward methods."""
+    cfg, model, reqs, _ = model_and_truth(name, "float32")
+    W = make_weights(cfg, CONFIGS[name][1])
+    ids = reqs["r61"]
+    _, layers = plain.forward(cfg, W, ids, collect_layers=True)
+    eng = engine_for(model, use_plan=False, use_graphs=False)
+    seen = []
+    originals = [b.forward for b in model.blocks]
+    try:
+        for b, orig in zip(model.blocks, originals):
+            def fw(x, step, caches, orig=orig):
+                orig(x, step, caches)
+                seen.append(x.tensor().clone())
+            b.forward = fw
+        from gibbs_b200 import StepEntry
+        eng.open("x")
+        eng.step([StepEntry("x", ids, [len(ids) - 1])])
+        eng.close("x")
+    finally:
+        for b in model.blocks:
+            del b.forward
+    assert len(seen) == len(cfg["layers"])
+    for i, x in enumerate(seen):
+        assert rel_rows(x.cpu(), layers[i]).max() <= 1e-4, f"layer {i}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_plan_and_forward_methods_give_the_same_bits(name, dtype):
+    cfg, model, reqs, _ = model_and_truth(name, dtype)
+    steps = trace_mixed(reqs, capacity_tokens=320, seed=3)
+    a = run_trace_on_engine(engine_for(model, n_pages=20), steps)
+    b = run_trace_on_engine(engine_for(model, n_pages=20, use_plan=False, use_graphs=False), steps)
+    for rid in reqs:
+        assert np.array_equal(a[rid], b[rid]), rid
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_mixed_batches_with_pages_and_slots_used_again(name, dtype):
+    """Up to three live requests in a pool that holds little more than the live ones, portions beside
+    single tokens: against the plain implementation, and against each request run alone."""
+    cfg, model, reqs, truth = model_and_truth(name, dtype)
+    more = dict(reqs)
+    for k in range(4):                                        # the same lengths again: slots and pages go round
+        more[f"again{k}"] = ids_for(cfg, 500 + k, 40 + 17 * k)
+    for seed in (0, 1):
+        eng = engine_for(model, n_pages=20, max_requests=3)   # 320 tokens of pages, 3 slots
+        got = run_trace_on_engine(eng, trace_mixed(more, capacity_tokens=320, max_live=3, seed=seed))
+        assert eng.cache.free_pages() == [20] * len(eng.cache.groups)
+        for rid in reqs:
+            check_rows(got[rid], truth[rid], dtype, strict=False, what=f"{name} mixed {rid}")
+        alone = run_trace_on_engine(engine_for(model), trace_whole(more))
+        for rid in more:
+            e = rel_rows(got[rid], alone[rid])
+            lim = 1e-4 if dtype == "float32" else TOL[dtype]
+            assert (e > lim).mean() <= (0.0 if dtype == "float32" else 0.45), f"{rid}: batch against alone {e.max():.3g}"
+
+
+def test_long_decoding_past_windows_pages_and_chunks():
+    """260 tokens decoded one by one after a two-token prompt: every window edge, page edge and slot
+    state is passed by single tokens."""
+    cfg, model, _, _ = model_and_truth("A", "float32")
+    W = make_weights(cfg, CONFIGS["A"][1])
+    ids = ids_for(cfg, 77, 262)
+    truth = plain.forward(cfg, W, ids).numpy()
+    eng = engine_for(model, n_pages=20)
+    got = run_trace_on_engine(eng, trace_tail_decoded({"long": ids}, tail=260))
+    e = rel_rows(got["long"], truth)
+    assert e.max() <= TOL["float32"], f"first wrong position {int(np.nonzero(e > TOL['float32'])[0][0])}"
+    # the windowed group has given back what the window passed
+    assert min(eng.cache.free_pages()) == 20
+
+
+def test_greedy_generation_through_the_scheduler():
+    """Generator -> Scheduler -> Engine.step -> sampler: the tokens are those the plain implementation
+    picks, fed back one by one; several prompts of unequal length at once."""
+    from gibbs_b200 import Generator, SamplingParams
+    cfg, model, _, _ = model_and_truth("B", "float32")
+    W = make_weights(cfg, CONFIGS["B"][1])
+    gen_ = Generator(model, ctx=256, page_size=16, n_pages=40, max_running=4, max_batch_tokens=48)
+    prompts = [ids_for(cfg, 900 + k, n) for k, n in enumerate((3, 50, 19))]
+    outs = gen_.generate(prompts, SamplingParams(max_new_tokens=12, temperature=0.0), stop_at_eos=False)
+    for p, out in zip(prompts, outs):
+        seq = list(p)
+        for tok in out:
+            logits = plain.forward(cfg, W, seq)[-1]
+            top2 = torch.topk(logits, 2).values
+            if float(top2[0] - top2[1]) > 1e-3:               # (no verdict on a tie)
+                assert int(logits.argmax()) == tok, f"after {len(seq)} tokens"
+            seq.append(tok)
+        assert len(out) == 12
