@@ -43,6 +43,66 @@ def reference_arm():
     return 0
 
 
+def potivik_shape(size: str) -> dict:
+    """Layer sizes that resemble a real model's, for the Potivik design: state-space and latent-attention
+    layers in turn, a dense gated unit behind the former and routed experts behind the latter."""
+    if size == "1k":
+        d, vocab, side = 1024, 32768, 128
+        ssm = {"heads": 32, "vdim": 64, "state": 64, "groups": 4, "conv": 4, "norm_groups": 4}
+        att = {"heads": 8, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256, "scale": 96 ** -0.5,
+               "mask": {"size": 512}, "rot": {"base": 500000.0, "dims": 32}}
+        dense = {"kind": "dense", "ff": 4096, "limit": 7.0}
+        moe = {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": 512, "limit": 7.0},
+               "shared": {"ff": 1024, "limit": 7.0}}
+    else:
+        d, vocab, side = 2048, 65536, 256
+        ssm = {"heads": 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}
+        att = {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
+               "mask": {"size": 1024}, "rot": {"base": 500000.0, "dims": 64}}
+        dense = {"kind": "dense", "ff": 8192, "limit": 7.0}
+        moe = {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": 1024, "limit": 7.0},
+               "shared": {"ff": 2048, "limit": 7.0}}
+    layers = []
+    for i in range(8):
+        layers.append({"type": "mamba2", "mixer": ssm, "mlp": dense} if i % 2 == 0 else
+                      {"type": "latent_attention", "mixer": att, "mlp": moe})
+    return {"architecture": "Potivik", "vocab": vocab, "width": d, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "token_side": {"dim": side}, "layers": layers}
+
+
+def potivik_workload(a):
+    """Prompt and decode throughput of the Potivik design at two sizes (random weights), beside an LFM2
+    model of equal width, depth and feed-forward width, with the time per kind of operation of one
+    prompt step and one decode step (the walker's timing mode).  One JSON line per model and size."""
+    import torch
+    from gibbs_b200 import Engine, Lfm2Config, parse_config, random_model
+    from gibbs_b200.engine import benchmark as B
+    prompt, batch, ctx = 2048, 8, 1024
+    for size in (a.size.split(",") if a.size else ["1k", "2k"]):
+        pot = potivik_shape(size)
+        d = pot["width"]
+        twin = dict(LFM2_1P2B, hidden_size=d, num_hidden_layers=8, num_attention_heads=d // 64, num_key_value_heads=d // 256,
+                    head_dim=64, vocab_size=pot["vocab"], intermediate_size=4 * d, block_auto_adjust_ff_dim=False,
+                    full_attn_idxs=[1, 3, 5, 7], max_position_embeddings=4096)
+        for name, conf in (("Potivik", parse_config(pot)), ("LFM2 of equal size", Lfm2Config.from_dict(twin))):
+            model = random_model(conf, SEED, dtype="bfloat16", device="cuda:0", stored_dtype=torch.bfloat16)
+            eng = Engine(model, n_pages=(batch + 1) * (4096 // 16), page_size=16, max_requests=batch, max_step_tokens=prompt,
+                         max_context=4096)
+            pre = B.measure_prefill(eng, prompt, warmup=3, runs=5, seed=SEED)
+            dec = B.measure_decode(eng, batch, ctx, a.steps, max(a.warmup, 3), seed=SEED)
+            line = {"model": name, "width": d, "layers": 8, "prompt_tokens": prompt, "prefill_ms": round(pre["ms"], 3),
+                    "prefill_tok_s": round(pre["value"], 1), "decode_batch": batch, "decode_context": dec["context"],
+                    "decode_ms_per_step": round(dec["ms_per_step"], 4), "decode_tok_s": round(dec["tok_s"], 1),
+                    "decode_gbs": round(dec["gbs"], 1), "launches_per_decode_step": dec["launches"] // max(a.steps, 1),
+                    "prefill_kind_ms": B.prefill_kind_times(eng, prompt, seed=SEED),
+                    "decode_kind_us": B.decode_kind_times(eng, batch, ctx, seed=SEED),
+                    "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02), uniform-random token ids"}
+            print(json.dumps(line), flush=True)
+            del eng, model
+            torch.cuda.empty_cache()
+    return 0
+
+
 def other_workload(a):
     """The two other workloads this project's configurations name: mixed serving at the
     LFM2-700M shape, and a long context at the LFM2-2.6B shape."""
@@ -115,8 +175,10 @@ def main():
                     help="float32: the engine's true 32-bit twin on the same (bfloat16-rounded) weights; "
                          "with --only prefill or --only decode (the benchmark line itself is bfloat16)")
     ap.add_argument("--skip-points", action="store_true", help="skip batch 1 and 64")
-    ap.add_argument("--workload", choices=["serve700m", "long2p6b", "sweep"], default=None,
-                    help="run one of the other reference workloads instead (prints its own JSON line)")
+    ap.add_argument("--workload", choices=["serve700m", "long2p6b", "sweep", "potivik"], default=None,
+                    help="run one of the other workloads instead (prints its own JSON lines); 'potivik': the Potivik "
+                         "design at layer sizes of a real model, beside an LFM2 model of equal size")
+    ap.add_argument("--size", default=None, help="with --workload potivik: '1k', '2k' or both with a comma (default both)")
     ap.add_argument("--prompt-tokens", type=int, default=None,
                     help="with --only prefill / prefill-timeline / products: another prompt length than 2,048")
     ap.add_argument("--only", default=None,
@@ -139,6 +201,8 @@ def main():
     from gibbs_b200 import Generator, Lfm2Config, random_model
     from gibbs_b200.engine import benchmark as B
 
+    if a.workload == "potivik":
+        return potivik_workload(a)
     if a.workload:
         return other_workload(a)
     raw = dict(LFM2_1P2B)

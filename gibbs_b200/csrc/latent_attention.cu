@@ -107,7 +107,7 @@ template <typename TC, int RL>
 __global__ void latent_attention_kernel(const float* qp, const TC* pages, const int* block_table, int bt_stride,
                                         int page_size, int n_pages, const int* tok_req, const int* tok_pos,
                                         const float* gate, long long ld_gate, float* out, long long ldo, int H, int r,
-                                        int dr, float scale, int window, int* status) {
+                                        int dr, float scale, int window, int splits, int chunk, float* ws, int* status) {
   extern __shared__ __align__(16) float smem[];
   pdl_trigger();
   const int Dk = r + dr, Dp = Dk + 1;
@@ -120,6 +120,9 @@ __global__ void latent_attention_kernel(const float* qp, const TC* pages, const 
   const int pos = tok_pos[t];
   const int* table = block_table + (size_t)tok_req[t] * bt_stride;
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  // this block's share of the visible keys lo .. pos: chunk number blockIdx.z, counted from lo
+  const int k_begin = splits > 1 ? lo + (int)blockIdx.z * chunk : lo;
+  const int k_end = splits > 1 ? min(pos, k_begin + chunk - 1) : pos;
   pdl_wait();
   for (int i = threadIdx.x; i < LA_HB * Dk; i += blockDim.x) {
     const int hh = h0 + i / Dk;
@@ -129,13 +132,13 @@ __global__ void latent_attention_kernel(const float* qp, const TC* pages, const 
 #pragma unroll
   for (int i = 0; i < RL; ++i) acc[i] = 0.f;
   const float* q = qs + warp * Dk;
-  for (int k0 = lo; k0 <= pos; k0 += LA_KT) {
+  for (int k0 = k_begin; k0 <= k_end; k0 += LA_KT) {
     __syncthreads();                       // the last tile has been used (and q is in place)
     for (int i = threadIdx.x; i < LA_KT * Dk; i += blockDim.x) {
       const int j = i / Dk, d = i - j * Dk;
       const int kp = k0 + j;
       float v = 0.f;
-      if (kp <= pos) {
+      if (kp <= k_end) {
         const int page = table[kp / page_size];
         if (page < 0 || page >= n_pages) {
           if (d == 0) atomicExch(status, STATUS_BAD_PAGE_READ);
@@ -148,7 +151,7 @@ __global__ void latent_attention_kernel(const float* qp, const TC* pages, const 
     __syncthreads();
     if (!live) continue;
     float s = -INFINITY;
-    if (k0 + lane <= pos) {
+    if (k0 + lane <= k_end) {
       const float* kr = ks + lane * Dp;
       float dot = 0.f;
       for (int d = 0; d < Dk; ++d) dot = fmaf(q[d], kr[d], dot);
@@ -156,12 +159,12 @@ __global__ void latent_attention_kernel(const float* qp, const TC* pages, const 
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float corr = expf(m - m_new);    // (0 on the first tile: m = -inf)
-    const float p = k0 + lane <= pos ? expf(s - m_new) : 0.f;
+    const float p = k0 + lane <= k_end ? expf(s - m_new) : 0.f;
     l = l * corr + warp_sum(p);
     m = m_new;
 #pragma unroll
     for (int i = 0; i < RL; ++i) acc[i] *= corr;
-    const int n_keys = min(LA_KT, pos - k0 + 1);
+    const int n_keys = min(LA_KT, k_end - k0 + 1);
     for (int j = 0; j < n_keys; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const float* kr = ks + j * Dp;
@@ -173,6 +176,17 @@ __global__ void latent_attention_kernel(const float* qp, const TC* pages, const 
     }
   }
   if (!live) return;
+  if (splits > 1) {
+    // partial result of this chunk: running maximum, sum of weights, weighted sum (not yet divided)
+    float* w = ws + (((size_t)t * H + h) * splits + blockIdx.z) * (r + 2);
+    if (lane == 0) { w[0] = m; w[1] = l; }
+#pragma unroll
+    for (int i = 0; i < RL; ++i) {
+      const int d = lane + 32 * i;
+      if (d < r) w[2 + d] = acc[i];
+    }
+    return;
+  }
   const float g = gate ? hy_sigmoid(gate[(size_t)t * ld_gate + h]) : 1.f;
   const float inv = g / l;
   float* o = out + (size_t)t * ldo + (size_t)h * r;
@@ -183,7 +197,60 @@ __global__ void latent_attention_kernel(const float* qp, const TC* pages, const 
   }
 }
 
+// One warp per (token, head): the chunks' partial results, merged in chunk order.
+__global__ void latent_attention_merge_kernel(const float* ws, int splits, const float* gate, long long ld_gate,
+                                              float* out, long long ldo, int n, int H, int r) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long idx = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (idx >= (long long)n * H) return;
+  const int t = (int)(idx / H), h = (int)(idx - (long long)t * H);
+  const float* w = ws + (size_t)idx * splits * (r + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, w[(size_t)s * (r + 2)]);
+  float L = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float m = w[(size_t)s * (r + 2)];
+    if (m > -INFINITY) L += expf(m - M) * w[(size_t)s * (r + 2) + 1];
+  }
+  const float g = gate ? hy_sigmoid(gate[(size_t)t * ld_gate + h]) : 1.f;
+  for (int d = lane; d < r; d += 32) {
+    float a = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float m = w[(size_t)s * (r + 2)];
+      if (m > -INFINITY) a += expf(m - M) * w[(size_t)s * (r + 2) + 2 + d];
+    }
+    out[(size_t)t * ldo + (size_t)h * r + d] = a * (g / L);
+  }
+}
+
 }  // namespace
+
+// How the visible keys of a launch are cut into chunks of whole key tiles: (chunks, keys per chunk).
+// Few tokens (decoding) get many chunks, so that the GPU is occupied; a launch with enough (token, head
+// group) blocks of its own gets one.  With a window the chunk depends on the launch's sizes only, not on
+// the contexts' lengths; chunks lie at fixed distances from the first visible key, so a chunk's partial
+// result does not depend on how many chunks there are.
+GB_API int gb_latent_attention_chunks(int n, int H, int window, int max_ctx, int* chunk_out) {
+  const int blocks = n * gb_div_up(H, 8);
+  int wanted = 592 / (blocks > 0 ? blocks : 1);
+  if (wanted > 64) wanted = 64;
+  const int span = window > 0 ? window : (max_ctx > 0 ? max_ctx : 1);
+  if (wanted <= 1 || span <= 64) { *chunk_out = span; return 1; }
+  int chunk;
+  if (window > 0) {
+    chunk = 32 * gb_div_up(gb_div_up(span, wanted), 32);
+    if (chunk < 64) chunk = 64;
+  } else {
+    chunk = 256;
+    while (gb_div_up(span, chunk) > 2 * wanted) chunk *= 2;
+  }
+  *chunk_out = chunk;
+  return gb_div_up(span, chunk);
+}
+// Rows of (latent size + 2) floats a launch's partial results may need, whatever its sizes.
+GB_API int gb_latent_attention_workspace_rows() { return 8 * 2 * (592 + 592); }
 
 // a0 fused rows [q heads (plain | rotated) | ... ] (f32), a1 their stride, a2 column of [latent | rotated key],
 // a3 gain of the latent's norm [r], a4 inv_freq [rot_dims / 2], a5 rot_dims, a6 token -> request, a7 token ->
@@ -225,14 +292,19 @@ GB_OP(gb_op_head_linear) {
 // a0 q' [tokens, heads, r + rot] (f32), a1 pages, a2 their dtype, a3 block table, a4 its entries per request, a5 page
 // size, a6 number of pages, a7 token -> request, a8 token -> position, a9 gate logits (f32, [t, h] at a row stride) or
 // 0, a10 that stride, a11 out [tokens, heads * r] (f32), a12 its row stride, a13 tokens, a14 heads, a15 latent size,
-// a16 rotated size, a17 window (0: every earlier position); f0 scale
+// a16 rotated size, a17 window (0: every earlier position), a18 longest context of the step (an upper bound will do),
+// a19 workspace for partial results, gb_latent_attention_workspace_rows() rows of (latent size + 2) floats; f0 scale
 GB_OP(gb_op_latent_attention) {
   const int n = (int)a[13], H = (int)a[14], r = (int)a[15], dr = (int)a[16];
   if (n <= 0) return 0;
   if (r > 512) GB_FAIL(GB_ERR_ARG, "latent_attention: latent size %d (at most 512)", r);
   const int Dk = r + dr;
   const size_t smem = sizeof(float) * ((size_t)LA_HB * Dk + (size_t)LA_KT * (Dk + 1));
-  const dim3 grid(n, gb_div_up(H, LA_HB)), block(32 * LA_HB);
+  int chunk = 0;
+  int splits = gb_latent_attention_chunks(n, H, (int)a[17], (int)a[18], &chunk);
+  float* ws = op_ptr<float>(a[19]);
+  if (ws == nullptr || (long long)n * H * splits > gb_latent_attention_workspace_rows()) splits = 1;
+  const dim3 grid(n, gb_div_up(H, LA_HB), splits), block(32 * LA_HB);
 #define LA(TC, RL)                                                                                                   \
   do {                                                                                                               \
     static size_t allowed = 48 * 1024;     /* raised once per size, before any stream capture replays the launch */ \
@@ -243,7 +315,7 @@ GB_OP(gb_op_latent_attention) {
     gb_launch(latent_attention_kernel<TC, RL>, grid, block, smem, ctx->stream, op_ptr<const float>(a[0]),             \
               op_ptr<const TC>(a[1]), op_ptr<const int>(a[3]), (int)a[4], (int)a[5], (int)a[6], op_ptr<const int>(a[7]), \
               op_ptr<const int>(a[8]), op_ptr<const float>(a[9]), a[10], op_ptr<float>(a[11]), a[12], H, r, dr,       \
-              (float)f[0], (int)a[17], ctx->status);                                                                 \
+              (float)f[0], (int)a[17], splits, chunk, ws, ctx->status);                                              \
   } while (0)
 #define LA_RL(TC)                                                                                                    \
   do {                                                                                                               \
@@ -254,5 +326,9 @@ GB_OP(gb_op_latent_attention) {
 #undef LA_RL
 #undef LA
   GB_CHECK_LAUNCH("latent_attention");
-  return 1;
+  if (splits == 1) return 1;
+  gb_launch(latent_attention_merge_kernel, dim3(gb_div_up((long long)n * H, 4)), dim3(128), 0, ctx->stream, ws, splits,
+            op_ptr<const float>(a[9]), a[10], op_ptr<float>(a[11]), a[12], n, H, r);
+  GB_CHECK_LAUNCH("latent_attention_merge");
+  return 2;
 }

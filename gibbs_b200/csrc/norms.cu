@@ -44,7 +44,7 @@ __global__ void row_norm_kernel(const float* x, long long ldx, const float* __re
 }
 
 __global__ void norm_add_kernel(float* x, long long ldx, const float* y, long long ldy, const float* __restrict__ gain,
-                                int dim, int kind, float eps) {
+                                int dim, int kind, float eps, bf16* copy) {
   __shared__ float scratch[32];
   pdl_trigger();
   pdl_wait();
@@ -52,7 +52,11 @@ __global__ void norm_add_kernel(float* x, long long ldx, const float* y, long lo
   float mean, rstd;
   row_stats(row, dim, kind, eps, scratch, mean, rstd);
   float* o = x + (size_t)blockIdx.x * ldx;
-  for (int d = threadIdx.x; d < dim; d += blockDim.x) o[d] += (row[d] - mean) * rstd * gain[d];
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    const float v = o[d] + (row[d] - mean) * rstd * gain[d];
+    o[d] = v;
+    if (copy) copy[(size_t)blockIdx.x * dim + d] = __float2bfloat16_rn(v);
+  }
 }
 
 template <typename TO>
@@ -69,7 +73,7 @@ __global__ void clamped_glu_kernel(const float* gu, long long ld, TO* out, long 
 
 template <typename TT>
 __global__ void gelu_mul_rows_kernel(float* g, long long ld, const TT* __restrict__ table, long long ldt, int offset,
-                                     const int* ids, int n, int dim, int vocab) {
+                                     const int* ids, int n, int dim, int vocab, bf16* out16) {
   pdl_trigger();
   pdl_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -78,7 +82,9 @@ __global__ void gelu_mul_rows_kernel(float* g, long long ld, const TT* __restric
   const int id = ids[t];
   const float e = (id >= 0 && id < vocab) ? to_f32(table[(size_t)id * ldt + offset + c]) : 0.f;
   float* p = g + (size_t)t * ld + c;
-  *p = hy_gelu_tanh(*p) * e;
+  const float v = hy_gelu_tanh(*p) * e;
+  if (out16) out16[(size_t)t * dim + c] = __float2bfloat16_rn(v);
+  else *p = v;
 }
 
 // one block per (row, group)
@@ -125,13 +131,14 @@ GB_OP(gb_op_row_norm) {
   return 1;
 }
 
-// a0 x (f32, the stream), a1 its row stride, a2 y (f32), a3 its row stride, a4 gain, a5 rows, a6 dim, a7 kind; f0 eps
+// a0 x (f32, the stream), a1 its row stride, a2 y (f32), a3 its row stride, a4 gain, a5 rows, a6 dim, a7 kind,
+// a8 a bfloat16 copy of the new rows [rows, dim] for a product that reads the stream next, or 0; f0 eps
 GB_OP(gb_op_norm_add) {
   const int n = (int)a[5], dim = (int)a[6], kind = (int)a[7];
   if (n <= 0) return 0;
   if (kind != NORM_LAYER && kind != NORM_RMS) GB_FAIL(GB_ERR_ARG, "norm_add: kind %d", kind);
   gb_launch(norm_add_kernel, dim3(n), dim3(norm_threads(dim)), 0, ctx->stream, op_ptr<float>(a[0]), a[1],
-            op_ptr<const float>(a[2]), a[3], op_ptr<const float>(a[4]), dim, kind, (float)f[0]);
+            op_ptr<const float>(a[2]), a[3], op_ptr<const float>(a[4]), dim, kind, (float)f[0], op_ptr<bf16>(a[8]));
   GB_CHECK_LAUNCH("norm_add");
   return 1;
 }
@@ -153,17 +160,17 @@ GB_OP(gb_op_clamped_glu) {
 }
 
 // a0 g (f32, in place), a1 its row stride, a2 table, a3 its dtype, a4 its row stride, a5 first column, a6 token ids,
-// a7 rows, a8 dim, a9 rows of the table
+// a7 rows, a8 dim, a9 rows of the table, a10 a bfloat16 output [rows, dim] instead of writing in place, or 0
 GB_OP(gb_op_gelu_mul_rows) {
   const int n = (int)a[7], dim = (int)a[8];
   if (n <= 0) return 0;
   const dim3 grid(gb_div_up((long long)n * dim, 256)), block(256);
   if (a[3] == GB_BF16)
     gb_launch(gelu_mul_rows_kernel<bf16>, grid, block, 0, ctx->stream, op_ptr<float>(a[0]), a[1], op_ptr<const bf16>(a[2]),
-              a[4], (int)a[5], op_ptr<const int>(a[6]), n, dim, (int)a[9]);
+              a[4], (int)a[5], op_ptr<const int>(a[6]), n, dim, (int)a[9], op_ptr<bf16>(a[10]));
   else
     gb_launch(gelu_mul_rows_kernel<float>, grid, block, 0, ctx->stream, op_ptr<float>(a[0]), a[1], op_ptr<const float>(a[2]),
-              a[4], (int)a[5], op_ptr<const int>(a[6]), n, dim, (int)a[9]);
+              a[4], (int)a[5], op_ptr<const int>(a[6]), n, dim, (int)a[9], op_ptr<bf16>(a[10]));
   GB_CHECK_LAUNCH("gelu_mul_rows");
   return 1;
 }

@@ -246,6 +246,53 @@ def decode_kind_shares(engine: Engine, batch: int, prompt_len: int, steps: int =
     return {k: round(ms / total, 4) for k, (_, ms) in sorted(table.items(), key=lambda kv: -kv[1][1])}
 
 
+def _kind_times(engine: Engine, run_steps, steps: int) -> dict:
+    """{kind of operation: time per step} over ``steps`` steps run by ``run_steps()`` in the walker's
+    timing mode (every operation bracketed by CUDA events, one after the other)."""
+    if engine.plan is None:
+        return {}
+    graphs, timing = engine.use_graphs, engine.timing
+    engine.use_graphs, engine.timing = False, True
+    engine.plan.set_timing(True)
+    try:
+        run_steps()
+        table = engine.plan.timing_table()
+    finally:
+        engine.plan.set_timing(False)
+        engine.use_graphs, engine.timing = graphs, timing
+    return {k: ms / steps for k, (_, ms) in sorted(table.items(), key=lambda kv: -kv[1][1])}
+
+
+def prefill_kind_times(engine: Engine, n_tokens: int, steps: int = 3, seed: int = 0) -> dict:
+    """Milliseconds per kind of operation in one whole-prompt step of ``n_tokens`` tokens."""
+    rng = np.random.default_rng(seed)
+
+    def run():
+        for _ in range(steps):
+            ids = rng.integers(0, engine.vocab_size, n_tokens).tolist()
+            engine.open("kind-bench")
+            engine.step([StepEntry("kind-bench", ids, [n_tokens - 1])])
+            engine.close("kind-bench")
+    run()                                   # (warm)
+    return {k: round(v, 4) for k, v in _kind_times(engine, run, steps).items()}
+
+
+def decode_kind_times(engine: Engine, batch: int, prompt_len: int, steps: int = 8, seed: int = 0) -> dict:
+    """Microseconds per kind of operation in one decode step of ``batch`` requests."""
+    first = fill_contexts(engine, batch, prompt_len, seed)
+    entries = [StepEntry(("bench", r), [t], [0]) for r, t in enumerate(first)]
+
+    def run():
+        for _ in range(steps):
+            engine.step(entries)
+    try:
+        run()
+        return {k: round(1e3 * v, 2) for k, v in _kind_times(engine, run, steps).items()}
+    finally:
+        for r in range(batch):
+            engine.close(("bench", r))
+
+
 def _decode_stepper(engine: Engine, batch: int, prompt_len: int, seed: int):
     """Requests with ``prompt_len``-token contexts and a function that runs one fed decode step."""
     first = fill_contexts(engine, batch, prompt_len, seed)

@@ -68,13 +68,19 @@ class SandwichResidual(Block):
     def _run(self, rn, x, caches, h_of):
         hidden = x.shape[1]
         y = rn.buffer("branch", hidden, torch.float32)
+        # a token input reads the stream through a product: in bfloat16 the norm that completes the
+        # stream also leaves the rows in that type
+        copy = None
+        if "token_input" in self.parts and self.rt.dtype == torch.bfloat16:
+            copy = rn.buffer("stream_rows", hidden, torch.bfloat16)
+        has_ffn = "ffn" in self.parts
         self.mixer.run(rn, h_of(self.mixer_norm), y, self.caches_of("mixer", caches))
-        self.mixer_post_norm.add_normed(rn, x, y)
-        if "ffn" in self.parts:
+        self.mixer_post_norm.add_normed(rn, x, y, None if has_ffn else copy)
+        if has_ffn:
             self.ffn.run(rn, h_of(self.ffn_norm), y, None)
-            self.ffn_post_norm.add_normed(rn, x, y)
+            self.ffn_post_norm.add_normed(rn, x, y, copy)
         if "token_input" in self.parts:
-            self.token_input.run(rn, x)
+            self.token_input.run(rn, x, copy)
 
     def forward(self, x, step, caches):
         rn, xt = Eager(self.rt, step), stream_tensor(x)

@@ -45,24 +45,24 @@ class ClampedGLU(BranchPart, FeedForward):
 
     def run(self, rn: Runner, h, out, caches=None):
         gu = rn.buffer("glu_gate_up", 2 * self.inner, torch.float32)
-        rn.linear(h, self.gate_up, None, gu)
+        rn.linear(h, self.gate_up, None, gu, role="glu_gate_up")
         act = rn.buffer("glu_act", self.inner)
         rn.op("clamped_glu", [gu.data_ptr(), gu.stride(0), act.data_ptr(), ops.dtype_code(act.dtype), act.stride(0),
                               rn.N, self.inner], [self.alpha, self.limit, self.up_add])
-        rn.linear(act, self.down, None, out)
+        rn.linear(act, self.down, None, out, role="glu_down")
 
 
 class RoutedGLU(BranchPart, FeedForward):
     @classmethod
     def declare(cls, params):
         h, E, f = params["hidden"], params["experts"], params["expert_inner"]
-        d = {"router": TensorDecl.of(E, h, role=VECTOR)}
+        d = {"router": TensorDecl.of(E, h)}
         for e in range(E):
             d.update({f"e{e}.gate": TensorDecl.of(f, h), f"e{e}.up": TensorDecl.of(f, h), f"e{e}.down": TensorDecl.of(h, f)})
         if params.get("shared_inner"):
             s = params["shared_inner"]
             d.update({"shared.gate": TensorDecl.of(s, h), "shared.up": TensorDecl.of(s, h),
-                      "shared.down": TensorDecl.of(h, s), "shared.sg": TensorDecl.of(1, h, role=VECTOR)})
+                      "shared.down": TensorDecl.of(h, s), "shared.sg": TensorDecl.of(1, h)})
         return d
 
     def __init__(self, params, tensors, rt):
@@ -77,12 +77,14 @@ class RoutedGLU(BranchPart, FeedForward):
         self.w_gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], 0) for e in range(E)]).contiguous()
         self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(E)]).contiguous()
         self.shared = None
-        rows = [tensors["router"].to(torch.float32)]
+        # (stored as the checkpoint has them: a product of two bfloat16 numbers is exact in the 32-bit
+        # accumulator, so the logits are 32-bit sums of exact products on the tensor cores as well)
+        rows = [tensors["router"]]
         if p.get("shared_inner"):
             self.shared = ClampedGLU({"hidden": self.hidden, "inner": int(p["shared_inner"]), "limit": float(p["shared_limit"]),
                                       "alpha": self.alpha, "up_add": self.up_add},
                                      {k: tensors["shared." + k] for k in ("gate", "up", "down")}, rt)
-            rows.append(tensors["shared.sg"].to(torch.float32).reshape(1, self.hidden))
+            rows.append(tensors["shared.sg"].reshape(1, self.hidden))
         # the router and the shared expert's gate in one small 32-bit product
         self.w_router = torch.cat(rows, 0).contiguous()
 
@@ -93,7 +95,7 @@ class RoutedGLU(BranchPart, FeedForward):
         """A step reads the router, the shared expert and the experts its tokens choose:
         at most n_tokens * top of them."""
         per_expert = (self.w_gate_up[0].numel() + self.w_down[0].numel()) * self.w_down.element_size()
-        total = min(self.E, n_tokens * self.top) * per_expert + self.w_router.numel() * 4
+        total = min(self.E, n_tokens * self.top) * per_expert + self.w_router.numel() * self.w_router.element_size()
         seen.update((self.w_gate_up.data_ptr(), self.w_down.data_ptr(), self.w_router.data_ptr()))
         if self.shared is not None:
             total += tensor_bytes(self.shared, seen)
@@ -103,7 +105,7 @@ class RoutedGLU(BranchPart, FeedForward):
         E, top, d, f = self.E, self.top, self.hidden, self.inner
         shared = self.shared is not None
         logits = rn.buffer("moe_logits", E + (1 if shared else 0), torch.float32)
-        rn.linear(h, self.w_router, None, logits)
+        rn.linear(h, self.w_router, None, logits, role="router")
         idx = rn.buffer("moe_choice", top, torch.int32)
         wts = rn.buffer("moe_weight", top, torch.float32)
         sg = rn.buffer("moe_shared_gate", 1, torch.float32)

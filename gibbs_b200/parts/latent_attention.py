@@ -30,6 +30,11 @@ from .base import Mixer, PagedRows, TensorDecl, VECTOR, register_part
 from .runner import BranchPart, Runner, keep
 
 
+def _workspace_rows() -> int:
+    from ..ops.library import library
+    return int(library(hybrid.LIBRARY).gb_latent_attention_workspace_rows())
+
+
 class LatentAttention(BranchPart, Mixer):
     @classmethod
     def declare(cls, params):
@@ -81,7 +86,7 @@ class LatentAttention(BranchPart, Mixer):
         H, dn, dr, dv, r = self.heads, self.dn, self.dr, self.dv, self.r
         F, Dk = self.fused.shape[0], r + dr
         fused = rn.buffer("la_fused", F, torch.float32)
-        rn.linear(h, self.fused, None, fused)
+        rn.linear(h, self.fused, None, fused, role="latent_in")
         qp = rn.buffer("la_query", H * Dk, torch.float32)
         table, bt_stride = rn.table(view)
         pages = view.pages
@@ -93,15 +98,16 @@ class LatentAttention(BranchPart, Mixer):
                               ops.dtype_code(self.uk_t.dtype), qp.data_ptr(), ops.F32, qp.stride(0), Dk, rn.N, H, r, dn],
               label="head_linear:absorb")
         lat = rn.buffer("la_latent_out", H * r, torch.float32)
+        ws = rn.buffer("la_partial", r + 2, torch.float32, fixed_rows=_workspace_rows())
         rn.op("latent_attention", [qp.data_ptr(), pages.data_ptr(), ops.dtype_code(pages.dtype), table, bt_stride,
                                    pages.shape[1], pages.shape[0], rn.tok_req, rn.tok_pos,
                                    fused.data_ptr() + 4 * self.gate_col, fused.stride(0), lat.data_ptr(), lat.stride(0),
-                                   rn.N, H, r, dr, self.window or 0], [self.scale])
+                                   rn.N, H, r, dr, self.window or 0, rn.max_context, ws.data_ptr()], [self.scale])
         o = rn.buffer("la_heads_out", H * dv)
         rn.op("head_linear", [lat.data_ptr(), lat.stride(0), r, keep(rn, self.uv), ops.dtype_code(self.uv.dtype),
                               o.data_ptr(), ops.dtype_code(o.dtype), o.stride(0), dv, rn.N, H, dv, r],
               label="head_linear:values")
-        rn.linear(o, self.o, None, out)
+        rn.linear(o, self.o, None, out, role="latent_out")
 
 
 register_part("mixer", "latent_attention", LatentAttention)

@@ -78,10 +78,12 @@ class RowNorm(Norm):
               [self.eps], label="row_norm")
         return out
 
-    def add_normed(self, rn: Runner, x: torch.Tensor, y: torch.Tensor) -> None:
-        """x += norm(y) * gain, for x the stream and y a sublayer's output (both float32)."""
+    def add_normed(self, rn: Runner, x: torch.Tensor, y: torch.Tensor, copy: torch.Tensor = None) -> None:
+        """x += norm(y) * gain, for x the stream and y a sublayer's output (both float32).  ``copy``
+        (bfloat16 [rows, dim], contiguous) also receives the new rows, for a product that reads
+        the stream next."""
         rn.op("norm_add", [x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), keep(rn, self.gain), rn.N, self.dim,
-                           self.KIND], [self.eps], label="norm_add")
+                           self.KIND, 0 if copy is None else copy.data_ptr()], [self.eps], label="norm_add")
 
     def forward(self, x, out=None, rows=None):
         x = stream_tensor(x)

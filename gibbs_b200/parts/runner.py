@@ -21,6 +21,7 @@ from .base import NotPlannable, Residual
 class Runner:
     # rows in the step, requests, wanted rows; addresses of the step's metadata
     N = R = W = 0
+    max_context = 0      # the longest context of the step after it (inside a CUDA graph: an upper bound)
     token_ids = tok_req = tok_pos = q_start = q_len = start_pos = want_rows = 0
 
     def buffer(self, name: str, width: int, dtype=None, per_token: int = 1, fixed_rows: Optional[int] = None):
@@ -28,8 +29,9 @@ class Runner:
         or ``fixed_rows`` rows whatever the step."""
         raise NotImplementedError
 
-    def linear(self, x, weight, bias, out) -> None:
-        """out = x weight^T (+ bias); the kernel is chosen by the operand types."""
+    def linear(self, x, weight, bias, out, role: str = "") -> None:
+        """out = x weight^T (+ bias); the kernel is chosen by the operand types.  ``role`` names
+        the product in the timing table."""
         raise NotImplementedError
 
     def op(self, name: str, a, f=(), label: str = "") -> None:
@@ -48,6 +50,7 @@ class Eager(Runner):
     def __init__(self, rt, step):
         self.rt, self.step = rt, step
         self.N, self.R, self.W = step.n_tokens, step.n_requests, step.n_want
+        self.max_context = max(int(step.max_ctx_len), 1)
         for k in ("token_ids", "tok_req", "tok_pos", "q_start", "q_len", "start_pos", "want_rows"):
             setattr(self, k, getattr(step, k).data_ptr())
 
@@ -55,7 +58,7 @@ class Eager(Runner):
         rows = fixed_rows if fixed_rows is not None else self.N * per_token
         return torch.empty(rows, int(width), dtype=dtype or self.rt.dtype, device=self.rt.device)
 
-    def linear(self, x, weight, bias, out):
+    def linear(self, x, weight, bias, out, role=""):
         ops.linear(x[:self.N] if x.shape[0] != self.N else x, weight, bias, out)
 
     def op(self, name, a, f=(), label=""):
@@ -77,14 +80,15 @@ class Planned(Runner):
         self.token_ids, self.tok_req, self.tok_pos = P.sym(P.S_TOKEN_IDS), P.sym(P.S_TOK_REQ), P.sym(P.S_TOK_POS)
         self.q_start, self.q_len, self.start_pos = P.sym(P.S_Q_START), P.sym(P.S_Q_LEN), P.sym(P.S_START_POS)
         self.want_rows = P.sym(P.S_WANT_ROWS)
+        self.max_context = P.sym(P.S_MAXCTX)
         self._P = P
 
     def buffer(self, name, width, dtype=None, per_token=1, fixed_rows=None):
         rows = fixed_rows if fixed_rows is not None else self.plan.cap * per_token
         return self.plan.buffer(f"{name}[{rows}]", width, dtype, rows=rows)
 
-    def linear(self, x, weight, bias, out):
-        self.plan.linear(x, weight, bias, out, "plain", role="hybrid")
+    def linear(self, x, weight, bias, out, role=""):
+        self.plan.linear(x, weight, bias, out, "plain", role=role or "plain")
 
     def op(self, name, a, f=(), label=""):
         self.plan.emit(hybrid.plan_id(name), list(a), list(f), label=label or name)

@@ -67,7 +67,7 @@ class StateSpaceMixer(BranchPart, Mixer):
         inner, ch, H, G, N = self.inner, self.channels, self.heads, self.G, self.N
         width = 2 * inner + 2 * G * N + H
         u = rn.buffer("ssm_in", width, torch.float32)
-        rn.linear(h, self.w_in, None, u)
+        rn.linear(h, self.w_in, None, u, role="ssm_in")
         xbc = rn.buffer("ssm_conv", ch, torch.float32)
         slots = rn.slots(conv)
         rn.op("causal_conv_silu", [u.data_ptr() + 4 * inner, u.stride(0), keep(rn, self.taps), keep(rn, self.conv_bias),
@@ -82,7 +82,7 @@ class StateSpaceMixer(BranchPart, Mixer):
         rn.op("gated_group_norm", [y.data_ptr(), y.stride(0), u.data_ptr(), u.stride(0), keep(rn, self.gain),
                                    o.data_ptr(), ops.dtype_code(o.dtype), o.stride(0), rn.N, inner, self.norm_groups],
               [self.eps])
-        rn.linear(o, self.w_out, None, out)
+        rn.linear(o, self.w_out, None, out, role="ssm_out")
 
 
 register_part("mixer", "state_space", StateSpaceMixer)

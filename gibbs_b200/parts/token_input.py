@@ -7,7 +7,8 @@ of a second embedding table and adds, after its feed-forward,
     x <- x + y / sqrt(mean(y^2) + eps) * gain
 
 to the stream x (an RMS norm with a plain gain, whatever the model's norm is).
-Both products read and write 32-bit values.
+In float32 both products read and write 32-bit values; in bfloat16 they read
+bfloat16 roundings of the stream and of g and accumulate in 32-bit.
 """
 from __future__ import annotations
 
@@ -45,13 +46,17 @@ class GatedTokenInput(Part):
         # (the table's rows a step gathers are not counted, as for the token embedding)
         return (self.gate.numel() + self.proj.numel()) * self.gate.element_size() + self.gain.numel() * 4
 
-    def run(self, rn: Runner, x: torch.Tensor) -> None:
+    def run(self, rn: Runner, x: torch.Tensor, x_rows: torch.Tensor = None) -> None:
+        """``x``: the stream (float32), which receives the result; ``x_rows``: the same rows in
+        bfloat16 when the caller has them (the products then run on the tensor cores)."""
         g = rn.buffer("token_input_gate", self.dim, torch.float32)
-        rn.linear(x, self.gate, None, g)
+        rn.linear(x if x_rows is None else x_rows, self.gate, None, g, role="token_input_gate")
+        g16 = None if x_rows is None else rn.buffer("token_input_gated", self.dim, torch.bfloat16)
         rn.op("gelu_mul_rows", [g.data_ptr(), g.stride(0), keep(rn, self.table), ops.dtype_code(self.table.dtype),
-                                self.table.stride(0), self.offset, rn.token_ids, rn.N, self.dim, self.vocab])
+                                self.table.stride(0), self.offset, rn.token_ids, rn.N, self.dim, self.vocab,
+                                0 if g16 is None else g16.data_ptr()])
         y = rn.buffer("branch", self.hidden, torch.float32)
-        rn.linear(g, self.proj, None, y)
+        rn.linear(g if g16 is None else g16, self.proj, None, y, role="token_input_proj")
         rn.op("norm_add", [x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), keep(rn, self.gain), rn.N,
                            self.hidden, hybrid.NORM_RMS], [self.eps], label="norm_add")
 
