@@ -99,7 +99,8 @@ __device__ __forceinline__ bool moe_tile(const int* offsets, int E, int tile, in
 // GLU: tile columns alternate gate, up, gate, up, ... of 32 features; out [rows, ff]
 template <typename TA, typename TW>
 __global__ void moe_experts_glu_kernel(const TA* rows, long long ldr, const TW* __restrict__ W, const int* offsets, int E,
-                                       TA* act, long long lda, int ff, int width, float alpha, float limit, float up_add) {
+                                       TA* act, long long lda, int ff, int width, float alpha, float limit, float up_add,
+                                       int blocks64) {
   pdl_trigger();
   pdl_wait();
   int e, r0, r1;
@@ -112,7 +113,9 @@ __global__ void moe_experts_glu_kernel(const TA* rows, long long ldr, const TW* 
       [&](int i) -> const TA* { return r0 + i < r1 ? rows + (size_t)(r0 + i) * ldr : nullptr; },
       [&](int j) -> const TW* {
         const int c = c0 + (j >> 1);
-        return c < ff ? wb + (size_t)((j & 1) * ff + c) * width : nullptr;
+        // rows [gate (ff) | up (ff)], or alternating in blocks of 64: gate 0-63, up 0-63, gate 64-127, ...
+        const size_t wrow = blocks64 ? (size_t)(c >> 6) * 128 + (j & 1) * 64 + (c & 63) : (size_t)(j & 1) * ff + c;
+        return c < ff ? wb + wrow * width : nullptr;
       },
       width, acc, ty, tx);
 #pragma unroll
@@ -211,8 +214,8 @@ GB_OP(gb_op_moe_gather) {
 
 // a0 input rows, a1 their stride, a2 their dtype, a3 weights [E, out features, in features], a4 their dtype,
 // a5 offsets [E + 1], a6 experts, a7 out, a8 its row stride, a9 tokens, a10 features out (GLU: ff), a11 features in,
-// a12 mode (0: GLU over [gate rows | up rows], out in the input's dtype; 1: plain, out f32), a13 top; f0 alpha,
-// f1 limit, f2 what is added to u
+// a12 mode (0: GLU over [gate rows | up rows], out in the input's dtype; 1: plain, out f32), a13 top, a14 (GLU) 1 when
+// gate and up rows alternate in blocks of 64 instead; f0 alpha, f1 limit, f2 what is added to u
 GB_OP(gb_op_moe_experts) {
   const int pairs = (int)(a[9] * a[13]), E = (int)a[6], n_out = (int)a[10], n_in = (int)a[11], mode = (int)a[12];
   if (pairs <= 0) return 0;
@@ -222,7 +225,7 @@ GB_OP(gb_op_moe_experts) {
 #define GLU(TA, TW)                                                                                                 \
   gb_launch(moe_experts_glu_kernel<TA, TW>, dim3(gb_div_up(n_out, 32), tiles), dim3(256), 0, ctx->stream,          \
             op_ptr<const TA>(a[0]), a[1], op_ptr<const TW>(a[3]), op_ptr<const int>(a[5]), E, op_ptr<TA>(a[7]), a[8], \
-            n_out, n_in, (float)f[0], (float)f[1], (float)f[2])
+            n_out, n_in, (float)f[0], (float)f[1], (float)f[2], (int)a[14])
 #define DOWN(TA, TW)                                                                                                \
   gb_launch(moe_experts_down_kernel<TA, TW>, dim3(gb_div_up(n_out, 64), tiles), dim3(256), 0, ctx->stream,         \
             op_ptr<const TA>(a[0]), a[1], op_ptr<const TW>(a[3]), op_ptr<const int>(a[5]), E, op_ptr<float>(a[7]),   \

@@ -21,7 +21,7 @@ from .library import check, library
 LIBRARY = "hybrid"
 OPERATIONS = ("row_norm", "norm_add", "clamped_glu", "gelu_mul_rows", "gated_group_norm", "causal_conv_silu",
               "ssm_scan", "latent_prep", "head_linear", "latent_attention", "moe_route", "moe_sort", "moe_gather",
-              "moe_experts", "moe_combine")
+              "moe_experts", "moe_experts_tc", "moe_combine")
 
 NORM_LAYER, NORM_RMS = 0, 1
 

@@ -16,11 +16,15 @@ ranges (csrc/moe.cu).
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from .. import ops
 from ..ops import hybrid
+from ..ops.library import library
 from .base import FeedForward, TensorDecl, VECTOR, register_part, tensor_bytes
+from .linear import interleave_gate_up
 from .runner import BranchPart, Runner, keep
 
 
@@ -74,7 +78,11 @@ class RoutedGLU(BranchPart, FeedForward):
         if not 1 <= self.top <= self.E:
             raise ValueError(f"top {self.top} of {self.E} experts")
         E = self.E
-        self.w_gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], 0) for e in range(E)]).contiguous()
+        # gate and up rows of an expert side by side; in blocks of 64 features where the width allows, the
+        # layout the tensor-core kernel's epilogue wants (csrc/moe_tc.cu)
+        self.blocks64 = self.inner % 64 == 0
+        join = interleave_gate_up if self.blocks64 else (lambda g, u: torch.cat([g, u], 0))
+        self.w_gate_up = torch.stack([join(tensors[f"e{e}.gate"], tensors[f"e{e}.up"]) for e in range(E)]).contiguous()
         self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(E)]).contiguous()
         self.shared = None
         # (stored as the checkpoint has them: a product of two bfloat16 numbers is exact in the 32-bit
@@ -120,13 +128,27 @@ class RoutedGLU(BranchPart, FeedForward):
                              rows.data_ptr(), rows.stride(0), rn.N, d, top])
         act = rn.buffer("moe_act", f, per_token=top)
         wdt = ops.dtype_code(self.w_down.dtype)
-        rn.op("moe_experts", [rows.data_ptr(), rows.stride(0), ops.dtype_code(rows.dtype), keep(rn, self.w_gate_up), wdt,
-                              offsets.data_ptr(), E, act.data_ptr(), act.stride(0), rn.N, f, d, 0, top],
-              [self.alpha, self.limit, self.up_add], label="moe_experts:gate_up")
         eout = rn.buffer("moe_expert_out", d, torch.float32, per_token=top)
-        rn.op("moe_experts", [act.data_ptr(), act.stride(0), ops.dtype_code(act.dtype), keep(rn, self.w_down), wdt,
-                              offsets.data_ptr(), E, eout.data_ptr(), eout.stride(0), rn.N, d, f, 1, top],
-              label="moe_experts:down")
+        lib = library(hybrid.LIBRARY)
+        tc = self.rt.dtype == torch.bfloat16 and self.w_down.dtype == torch.bfloat16
+        up_tc = tc and self.blocks64 and lib.gb_moe_experts_tc_supported(0, f, d, ctypes.c_longlong(rows.stride(0)), ctypes.c_longlong(d))
+        down_tc = tc and lib.gb_moe_experts_tc_supported(1, d, f, ctypes.c_longlong(act.stride(0)), ctypes.c_longlong(f))
+        if up_tc:
+            rn.op("moe_experts_tc", [rows.data_ptr(), rows.stride(0), rows.shape[0], keep(rn, self.w_gate_up), 0,
+                                     offsets.data_ptr(), E, act.data_ptr(), act.stride(0), rn.N, f, d, 0, top],
+                  [self.alpha, self.limit, self.up_add], label="moe_experts:gate_up")
+        else:
+            rn.op("moe_experts", [rows.data_ptr(), rows.stride(0), ops.dtype_code(rows.dtype), keep(rn, self.w_gate_up),
+                                  wdt, offsets.data_ptr(), E, act.data_ptr(), act.stride(0), rn.N, f, d, 0, top,
+                                  int(self.blocks64)], [self.alpha, self.limit, self.up_add], label="moe_experts:gate_up")
+        if down_tc:
+            rn.op("moe_experts_tc", [act.data_ptr(), act.stride(0), act.shape[0], keep(rn, self.w_down), 0,
+                                     offsets.data_ptr(), E, eout.data_ptr(), eout.stride(0), rn.N, d, f, 1, top],
+                  label="moe_experts:down")
+        else:
+            rn.op("moe_experts", [act.data_ptr(), act.stride(0), ops.dtype_code(act.dtype), keep(rn, self.w_down), wdt,
+                                  offsets.data_ptr(), E, eout.data_ptr(), eout.stride(0), rn.N, d, f, 1, top, 0],
+                  label="moe_experts:down")
         sh = None
         if shared:
             sh = rn.buffer("moe_shared_out", d, torch.float32)

@@ -229,8 +229,15 @@ def _routed_params(f, d):
             "shared_limit": sh["limit"] if sh else 0.0}
 
 
+# experts whose width is a multiple of 64: in bfloat16 their products run on the tensor cores (tiles of 64 rows
+# for the batch, of 16 for single tokens), in float32 on the 32-bit tiles with the same weight layout
+CFG_WIDE_EXPERTS = {"vocab": 16, "width": 64, "norm": {"eps": 1e-5}, "layers": [
+    {"type": "mamba2", "mixer": {"heads": 1, "vdim": 8, "state": 8, "groups": 1, "conv": 2, "norm_groups": 1},
+     "mlp": {"kind": "moe", "router": {"experts": 4, "top": 2}, "expert": {"ff": 128, "limit": 1.5}}}]}
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("cfg,layer", [(CFG_A, 0), (CFG_A, 3), (CFG_B, 0)])
+@pytest.mark.parametrize("cfg,layer", [(CFG_A, 0), (CFG_A, 3), (CFG_B, 0), (CFG_WIDE_EXPERTS, 0)])
 def test_routed_experts_alone(cfg, layer, dtype):
     f, d = cfg["layers"][layer]["mlp"], cfg["width"]
     W = plain.sub(make_weights(cfg, 13), f"l{layer}.mlp.")
