@@ -98,6 +98,37 @@ __global__ void head_linear_kernel(const float* x, long long ldx, long long xh, 
   }
 }
 
+// A cache row into shared memory as 32-bit values, 16 bytes at a time; `sub` of eight threads share the row.
+__device__ __forceinline__ void load_row_vec(const bf16* src, float* dst, int Dk, int sub) {
+  // (up to four pieces are requested before any is stored: a store to shared memory in between would make
+  // every load wait for the one before it)
+  for (int d0 = sub * 8; d0 < Dk; d0 += 256) {
+    uint4 raw[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (d0 + 64 * u < Dk) raw[u] = *reinterpret_cast<const uint4*>(src + d0 + 64 * u);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int d = d0 + 64 * u;
+      if (d < Dk) {
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f2 = __bfloat1622float2(h2[e]);
+          dst[d + 2 * e] = f2.x;
+          dst[d + 2 * e + 1] = f2.y;
+        }
+      }
+    }
+  }
+}
+__device__ __forceinline__ void load_row_vec(const float* src, float* dst, int Dk, int sub) {
+  for (int d = sub * 4; d < Dk; d += 32) {
+    const float4 v = *reinterpret_cast<const float4*>(src + d);
+    dst[d] = v.x; dst[d + 1] = v.y; dst[d + 2] = v.z; dst[d + 3] = v.w;
+  }
+}
+
 // One block per (token, group of up to HB heads); one warp per head.  Key rows arrive in tiles of 32
 // in shared memory (32-bit), shared by the block's heads.  Lane j scores key j of the tile; the output's
 // columns are spread over the lanes (RL per lane).
@@ -120,6 +151,8 @@ __global__ void latent_attention_kernel(const float* qp, const TC* pages, const 
   const int pos = tok_pos[t];
   const int* table = block_table + (size_t)tok_req[t] * bt_stride;
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  // rows of pages can be read in 16-byte pieces when their length allows (pages are 16-byte aligned)
+  const bool vec = (Dk * (int)sizeof(TC)) % 16 == 0 && (((uintptr_t)pages) & 15) == 0;
   // this block's share of the visible keys lo .. pos: chunk number blockIdx.z, counted from lo
   const int k_begin = splits > 1 ? lo + (int)blockIdx.z * chunk : lo;
   const int k_end = splits > 1 ? min(pos, k_begin + chunk - 1) : pos;
@@ -134,28 +167,44 @@ __global__ void latent_attention_kernel(const float* qp, const TC* pages, const 
   const float* q = qs + warp * Dk;
   for (int k0 = k_begin; k0 <= k_end; k0 += LA_KT) {
     __syncthreads();                       // the last tile has been used (and q is in place)
-    for (int i = threadIdx.x; i < LA_KT * Dk; i += blockDim.x) {
-      const int j = i / Dk, d = i - j * Dk;
+    {
+      // eight threads share a key row; its page is looked up once
+      const int j = threadIdx.x >> 3, sub = threadIdx.x & 7;
       const int kp = k0 + j;
-      float v = 0.f;
+      const TC* src = nullptr;
       if (kp <= k_end) {
         const int page = table[kp / page_size];
         if (page < 0 || page >= n_pages) {
-          if (d == 0) atomicExch(status, STATUS_BAD_PAGE_READ);
+          if (sub == 0) atomicExch(status, STATUS_BAD_PAGE_READ);
         } else {
-          v = to_f32(pages[((size_t)page * page_size + kp % page_size) * Dk + d]);
+          src = pages + ((size_t)page * page_size + kp % page_size) * Dk;
         }
       }
-      ks[j * Dp + d] = v;
+      float* dst = ks + j * Dp;
+      if (src == nullptr) {
+        for (int d = sub; d < Dk; d += 8) dst[d] = 0.f;
+      } else if (vec) {
+        load_row_vec(src, dst, Dk, sub);
+      } else {
+        for (int d = sub; d < Dk; d += 8) dst[d] = to_f32(src[d]);
+      }
     }
     __syncthreads();
     if (!live) continue;
     float s = -INFINITY;
     if (k0 + lane <= k_end) {
       const float* kr = ks + lane * Dp;
-      float dot = 0.f;
-      for (int d = 0; d < Dk; ++d) dot = fmaf(q[d], kr[d], dot);
-      s = dot * scale;
+      // four partial sums, so that the additions do not wait for one another; added in a fixed order
+      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+      int d = 0;
+      for (; d + 4 <= Dk; d += 4) {
+        d0 = fmaf(q[d], kr[d], d0);
+        d1 = fmaf(q[d + 1], kr[d + 1], d1);
+        d2 = fmaf(q[d + 2], kr[d + 2], d2);
+        d3 = fmaf(q[d + 3], kr[d + 3], d3);
+      }
+      for (; d < Dk; ++d) d0 = fmaf(q[d], kr[d], d0);
+      s = ((d0 + d1) + (d2 + d3)) * scale;
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float corr = expf(m - m_new);    // (0 on the first tile: m = -inf)

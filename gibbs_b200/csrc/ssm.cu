@@ -54,7 +54,10 @@ __global__ void conv_state_update_kernel(const float* in, long long ld, float* s
 }
 
 // Block: 4 warps, each with PC columns p of one head; lane l holds S[p][n] for n = l + 32 i, i < NPL.
-constexpr int SCAN_WARPS = 4, SCAN_PC = 2;
+// The inputs of SCAN_TOKENS tokens at a time are staged in shared memory by the whole block (B and C of
+// the head's group, the block's columns of x, the step size and the decay), so that the recurrence
+// itself reads nothing from global memory.
+constexpr int SCAN_WARPS = 4, SCAN_PC = 2, SCAN_COLS = SCAN_WARPS * SCAN_PC, SCAN_TOKENS = 16;
 
 template <int NPL>
 __global__ void ssm_scan_kernel(const float* xbc, long long ld, const float* dt_raw, long long ld_dt,
@@ -62,17 +65,22 @@ __global__ void ssm_scan_kernel(const float* xbc, long long ld, const float* dt_
                                 const float* __restrict__ dskip, float* state, long long slot_stride,
                                 const int* slot_ids, const int* q_start, const int* q_len, float* y, long long ldy, int H,
                                 int P, int N, int G) {
+  extern __shared__ float staged[];
+  float* sB = staged;                                   // [SCAN_TOKENS][N]  (B, not yet times dt)
+  float* sC = sB + SCAN_TOKENS * N;                     // [SCAN_TOKENS][N]
+  float* sX = sC + SCAN_TOKENS * N;                     // [SCAN_TOKENS][SCAN_COLS]
+  float* sDt = sX + SCAN_TOKENS * SCAN_COLS;            // [SCAN_TOKENS] step size
+  float* sDecay = sDt + SCAN_TOKENS;                    // [SCAN_TOKENS]
   pdl_trigger();
   const int r = blockIdx.x, h = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int p0 = (blockIdx.z * SCAN_WARPS + warp) * SCAN_PC;
+  const int pb = blockIdx.z * SCAN_COLS, p0 = pb + warp * SCAN_PC;
   const int g = h / (H / G);
   const int inner = H * P;
   const float bias = dt_bias[h], neg_a = -expf(a_log[h]), dsk = dskip[h];
   const int first = q_start[r], len = q_len[r];
   float* S = state + (size_t)slot_ids[r] * slot_stride + (size_t)h * P * N;
   pdl_wait();
-  if (p0 >= P) return;
   float s[SCAN_PC][NPL];
 #pragma unroll
   for (int c = 0; c < SCAN_PC; ++c)
@@ -81,29 +89,62 @@ __global__ void ssm_scan_kernel(const float* xbc, long long ld, const float* dt_
       const int n = lane + 32 * i;
       s[c][i] = (p0 + c < P && n < N) ? S[(size_t)(p0 + c) * N + n] : 0.f;
     }
-  for (int t = 0; t < len; ++t) {
-    const float* row = xbc + (size_t)(first + t) * ld;
-    const float dt = hy_softplus(dt_raw[(size_t)(first + t) * ld_dt + h] + bias);
-    const float decay = expf(neg_a * dt);
-    float bv[NPL], cv[NPL];
+  for (int t0 = 0; t0 < len; t0 += SCAN_TOKENS) {
+    const int nt = min(SCAN_TOKENS, len - t0);
+    __syncthreads();                                    // the chunk before has been used
+    // (four loads of B and of C are requested before any is stored: a store to shared memory in between
+    // would make every load wait for the one before it)
+    for (int i0 = threadIdx.x; i0 < nt * N; i0 += 4 * blockDim.x) {
+      float b[4], c[4];
 #pragma unroll
-    for (int i = 0; i < NPL; ++i) {
-      const int n = lane + 32 * i;
-      bv[i] = n < N ? row[inner + g * N + n] * dt : 0.f;
-      cv[i] = n < N ? row[inner + (G + g) * N + n] : 0.f;
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        b[u] = c[u] = 0.f;
+        if (i < nt * N) {
+          const int tt = i / N, n = i - tt * N;
+          const float* row = xbc + (size_t)(first + t0 + tt) * ld + inner;
+          b[u] = row[g * N + n];
+          c[u] = row[(G + g) * N + n];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < nt * N) { sB[i] = b[u]; sC[i] = c[u]; }
+      }
     }
-#pragma unroll
-    for (int c = 0; c < SCAN_PC; ++c) {
-      const int p = p0 + c;
-      const float xv = p < P ? row[h * P + p] : 0.f;
-      float part = 0.f;
+    for (int i = threadIdx.x; i < nt * SCAN_COLS; i += blockDim.x) {
+      const int tt = i / SCAN_COLS, c = i - tt * SCAN_COLS;
+      sX[i] = pb + c < P ? xbc[(size_t)(first + t0 + tt) * ld + h * P + pb + c] : 0.f;
+    }
+    if ((int)threadIdx.x < nt) {
+      const float dt = hy_softplus(dt_raw[(size_t)(first + t0 + threadIdx.x) * ld_dt + h] + bias);
+      sDt[threadIdx.x] = dt;
+      sDecay[threadIdx.x] = expf(neg_a * dt);
+    }
+    __syncthreads();
+    if (p0 >= P) continue;                              // (a warp without columns only helps to stage)
+    for (int tt = 0; tt < nt; ++tt) {
+      const float dt = sDt[tt], decay = sDecay[tt];
+      float bv[NPL], cv[NPL];
 #pragma unroll
       for (int i = 0; i < NPL; ++i) {
-        s[c][i] = fmaf(decay, s[c][i], bv[i] * xv);
-        part = fmaf(s[c][i], cv[i], part);
+        const int n = lane + 32 * i;
+        bv[i] = n < N ? sB[tt * N + n] * dt : 0.f;
+        cv[i] = n < N ? sC[tt * N + n] : 0.f;
       }
-      part = warp_sum(part);
-      if (lane == 0 && p < P) y[(size_t)(first + t) * ldy + h * P + p] = part + dsk * xv;
+#pragma unroll
+      for (int c = 0; c < SCAN_PC; ++c) {
+        const float xv = sX[tt * SCAN_COLS + warp * SCAN_PC + c];
+        float part = 0.f;
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) {
+          s[c][i] = fmaf(decay, s[c][i], bv[i] * xv);
+          part = fmaf(s[c][i], cv[i], part);
+        }
+        part = warp_sum(part);
+        if (lane == 0 && p0 + c < P) y[(size_t)(first + t0 + tt) * ldy + h * P + p0 + c] = part + dsk * xv;
+      }
     }
   }
 #pragma unroll
@@ -146,9 +187,10 @@ GB_OP(gb_op_ssm_scan) {
   if (R <= 0) return 0;
   if (G <= 0 || H % G) GB_FAIL(GB_ERR_ARG, "ssm_scan: %d heads in %d groups", H, G);
   if (N > 256) GB_FAIL(GB_ERR_ARG, "ssm_scan: state size %d (at most 256)", N);
-  const dim3 grid(R, H, gb_div_up(P, SCAN_WARPS * SCAN_PC)), block(32 * SCAN_WARPS);
+  const dim3 grid(R, H, gb_div_up(P, SCAN_COLS)), block(32 * SCAN_WARPS);
+  const size_t smem = sizeof(float) * (size_t)SCAN_TOKENS * (2 * N + SCAN_COLS + 2);      // at most 34 KB
 #define SCAN_LAUNCH(NPL)                                                                                              \
-  gb_launch(ssm_scan_kernel<NPL>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], op_ptr<const float>(a[2]), \
+  gb_launch(ssm_scan_kernel<NPL>, grid, block, smem, ctx->stream, op_ptr<const float>(a[0]), a[1], op_ptr<const float>(a[2]), \
             a[3], op_ptr<const float>(a[4]), op_ptr<const float>(a[5]), op_ptr<const float>(a[6]), op_ptr<float>(a[7]),   \
             a[8], op_ptr<const int>(a[9]), op_ptr<const int>(a[10]), op_ptr<const int>(a[11]), op_ptr<float>(a[12]),    \
             a[13], H, P, N, G)
