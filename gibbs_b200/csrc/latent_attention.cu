@@ -98,6 +98,45 @@ __global__ void head_linear_kernel(const float* x, long long ldx, long long xh, 
   }
 }
 
+// A few rows (decoding): one block per (8 outputs, head), the head's inputs of all rows in shared memory,
+// one warp per output with the lanes over the inputs.
+constexpr int HL_SMALL_ROWS = 16;
+
+template <typename TW, typename TO>
+__global__ void head_linear_small_kernel(const float* x, long long ldx, long long xh, const TW* __restrict__ W, TO* out,
+                                         long long ldo, long long oh, int n, int O, int I) {
+  extern __shared__ float xs[];                          // [n][I]
+  pdl_trigger();
+  pdl_wait();
+  const int h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < n * I; i += blockDim.x) {
+    const int t = i / I;
+    xs[i] = x[(size_t)t * ldx + (size_t)h * xh + (i - t * I)];
+  }
+  __syncthreads();
+  {
+    const int o = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (o >= O) return;
+    const TW* w = W + ((size_t)h * O + o) * I;
+    float acc[HL_SMALL_ROWS];
+#pragma unroll
+    for (int t = 0; t < HL_SMALL_ROWS; ++t) acc[t] = 0.f;
+    for (int i = lane; i < I; i += 32) {
+      const float wv = to_f32(w[i]);
+#pragma unroll
+      for (int t = 0; t < HL_SMALL_ROWS; ++t)
+        if (t < n) acc[t] = fmaf(xs[t * I + i], wv, acc[t]);
+    }
+#pragma unroll
+    for (int t = 0; t < HL_SMALL_ROWS; ++t) {
+      if (t < n) {
+        const float v = warp_sum(acc[t]);
+        if (lane == 0) out[(size_t)t * ldo + (size_t)h * oh + o] = from_f32<TO>(v);
+      }
+    }
+  }
+}
+
 // A cache row into shared memory as 32-bit values, 16 bytes at a time; `sub` of eight threads share the row.
 __device__ __forceinline__ void load_row_vec(const bf16* src, float* dst, int Dk, int sub) {
   // (up to four pieces are requested before any is stored: a store to shared memory in between would make
@@ -157,9 +196,18 @@ __global__ void latent_attention_kernel(const float* qp, const TC* pages, const 
   const int k_begin = splits > 1 ? lo + (int)blockIdx.z * chunk : lo;
   const int k_end = splits > 1 ? min(pos, k_begin + chunk - 1) : pos;
   pdl_wait();
-  for (int i = threadIdx.x; i < LA_HB * Dk; i += blockDim.x) {
-    const int hh = h0 + i / Dk;
-    qs[i] = hh < H ? qp[((size_t)t * H + hh) * Dk + (i % Dk)] : 0.f;
+  {
+    // this warp's query: four values are requested before any is stored (see load_row_vec)
+    const float* src = qp + ((size_t)t * H + (live ? h : 0)) * Dk;
+    float* dst = qs + warp * Dk;
+    for (int d0 = lane; d0 < Dk; d0 += 128) {
+      float v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = (live && d0 + 32 * u < Dk) ? src[d0 + 32 * u] : 0.f;
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (d0 + 32 * u < Dk) dst[d0 + 32 * u] = v[u];
+    }
   }
   float m = -INFINITY, l = 0.f, acc[RL];
 #pragma unroll
@@ -327,12 +375,19 @@ GB_OP(gb_op_latent_prep) {
 GB_OP(gb_op_head_linear) {
   const int n = (int)a[9], H = (int)a[10], O = (int)a[11], I = (int)a[12];
   if (n <= 0) return 0;
-  const dim3 grid(gb_div_up(O, 64), gb_div_up(n, 64), H), block(256);
+  const bool small = n <= HL_SMALL_ROWS && (size_t)n * I * sizeof(float) <= 48 * 1024;
+  const dim3 grid = small ? dim3(gb_div_up(O, 8), H) : dim3(gb_div_up(O, 64), gb_div_up(n, 64), H);
+  const dim3 block(256);
+  const size_t smem = small ? (size_t)n * I * sizeof(float) : 0;
 #define HL(TW, TO)                                                                                                  \
-  gb_launch(head_linear_kernel<TW, TO>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], a[2],         \
-            op_ptr<const TW>(a[3]), op_ptr<TO>(a[5]), a[7], a[8], n, O, I)
-  if (a[4] == GB_BF16) { if (a[6] == GB_BF16) HL(bf16, bf16); else HL(bf16, float); }
-  else { if (a[6] == GB_BF16) HL(float, bf16); else HL(float, float); }
+  if (small)                                                                                                        \
+    gb_launch(head_linear_small_kernel<TW, TO>, grid, block, smem, ctx->stream, op_ptr<const float>(a[0]), a[1], a[2], \
+              op_ptr<const TW>(a[3]), op_ptr<TO>(a[5]), a[7], a[8], n, O, I);                                        \
+  else                                                                                                              \
+    gb_launch(head_linear_kernel<TW, TO>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1], a[2],       \
+              op_ptr<const TW>(a[3]), op_ptr<TO>(a[5]), a[7], a[8], n, O, I)
+  if (a[4] == GB_BF16) { if (a[6] == GB_BF16) { HL(bf16, bf16); } else { HL(bf16, float); } }
+  else { if (a[6] == GB_BF16) { HL(float, bf16); } else { HL(float, float); } }
 #undef HL
   GB_CHECK_LAUNCH("head_linear");
   return 1;

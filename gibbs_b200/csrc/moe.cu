@@ -18,27 +18,37 @@ namespace {
 
 constexpr int MOE_MAX_EXPERTS = 1024;
 
+// one warp per token: lane l looks after experts l, l + 32, ... (a bit per expert it has given away)
 __global__ void moe_route_kernel(const float* logits, long long ld, int n, int E, int top, int shared_col, int* idx,
                                  float* weight, float* shared_gate) {
   pdl_trigger();
   pdl_wait();
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= n) return;
   const float* z = logits + (size_t)t * ld;
+  unsigned taken = 0;
   for (int k = 0; k < top; ++k) {
-    int best = -1;
-    float bv = 0.f;
-    for (int e = 0; e < E; ++e) {
-      bool taken = false;
-      for (int j = 0; j < k; ++j) taken |= idx[(size_t)t * top + j] == e;
-      if (taken) continue;
+    float bv = -INFINITY;
+    int be = 0x7fffffff;
+    for (int i = 0, e = lane; e < E; ++i, e += 32) {
+      if ((taken >> i) & 1u) continue;
       const float v = z[e];
-      if (best < 0 || v > bv) { best = e; bv = v; }
+      if (v > bv || be == 0x7fffffff) { bv = v; be = e; }   // (ascending e: a tie keeps the lower index)
     }
-    idx[(size_t)t * top + k] = best;
-    weight[(size_t)t * top + k] = hy_sigmoid(bv);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (oe != 0x7fffffff && (be == 0x7fffffff || ov > bv || (ov == bv && oe < be))) { bv = ov; be = oe; }
+    }
+    if ((be & 31) == lane) taken |= 1u << (be >> 5);
+    if (lane == 0) {
+      idx[(size_t)t * top + k] = be;
+      weight[(size_t)t * top + k] = hy_sigmoid(bv);
+    }
   }
-  if (shared_gate) shared_gate[t] = hy_sigmoid(z[shared_col]);
+  if (shared_gate && lane == 0) shared_gate[t] = hy_sigmoid(z[shared_col]);
 }
 
 // one block
@@ -179,7 +189,8 @@ GB_OP(gb_op_moe_route) {
   const int n = (int)a[2], E = (int)a[3], top = (int)a[4];
   if (n <= 0) return 0;
   if (top < 1 || top > E) GB_FAIL(GB_ERR_ARG, "moe_route: top %d of %d experts", top, E);
-  gb_launch(moe_route_kernel, dim3(gb_div_up(n, 128)), dim3(128), 0, ctx->stream, op_ptr<const float>(a[0]), a[1], n, E,
+  if (E > MOE_MAX_EXPERTS) GB_FAIL(GB_ERR_ARG, "moe_route: %d experts (at most %d)", E, MOE_MAX_EXPERTS);
+  gb_launch(moe_route_kernel, dim3(gb_div_up(n, 4)), dim3(128), 0, ctx->stream, op_ptr<const float>(a[0]), a[1], n, E,
             top, (int)a[5], op_ptr<int>(a[6]), op_ptr<float>(a[7]), op_ptr<float>(a[8]));
   GB_CHECK_LAUNCH("moe_route");
   return 1;

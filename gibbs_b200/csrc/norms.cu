@@ -12,19 +12,53 @@ namespace {
 
 enum { NORM_LAYER = 0, NORM_RMS = 1 };
 
-// mean and 1/sqrt(var + eps) of a row of `dim` floats; every thread of the block gets both.
-__device__ __forceinline__ void row_stats(const float* row, int dim, int kind, float eps, float* scratch, float& mean,
-                                          float& rstd) {
+// Rows of up to NORM_CACHE * blockDim.x values are read once and kept in registers; longer rows are read
+// again from memory (an L2 hit) for every pass.
+constexpr int NORM_CACHE = 8;
+
+struct RowCache {
+  float v[NORM_CACHE];
+  bool whole;
+};
+
+__device__ __forceinline__ void row_load(const float* row, int dim, RowCache& c) {
+  c.whole = dim <= NORM_CACHE * (int)blockDim.x;
+  if (c.whole) {
+#pragma unroll
+    for (int i = 0; i < NORM_CACHE; ++i) {
+      const int d = threadIdx.x + i * blockDim.x;
+      c.v[i] = d < dim ? row[d] : 0.f;
+    }
+  }
+}
+
+// mean and 1/sqrt(var + eps) of a row of `dim` floats (the variance is the mean of the squared deviations,
+// taken in a second pass); every thread of the block gets both.
+__device__ __forceinline__ void row_stats(const float* row, const RowCache& c, int dim, int kind, float eps,
+                                          float* scratch, float& mean, float& rstd) {
   mean = 0.f;
   if (kind == NORM_LAYER) {
     float s = 0.f;
-    for (int d = threadIdx.x; d < dim; d += blockDim.x) s += row[d];
+    if (c.whole) {
+#pragma unroll
+      for (int i = 0; i < NORM_CACHE; ++i) s += c.v[i];
+    } else {
+      for (int d = threadIdx.x; d < dim; d += blockDim.x) s += row[d];
+    }
     mean = block_sum(s, scratch) / (float)dim;
   }
   float ss = 0.f;
-  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-    const float v = row[d] - mean;
-    ss += v * v;
+  if (c.whole) {
+#pragma unroll
+    for (int i = 0; i < NORM_CACHE; ++i) {
+      const float v = (int)(threadIdx.x + i * blockDim.x) < dim ? c.v[i] - mean : 0.f;
+      ss += v * v;
+    }
+  } else {
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+      const float v = row[d] - mean;
+      ss += v * v;
+    }
   }
   rstd = 1.0f / sqrtf(block_sum(ss, scratch) / (float)dim + eps);
 }
@@ -34,13 +68,24 @@ __global__ void row_norm_kernel(const float* x, long long ldx, const float* __re
                                 int dim, int kind, float eps) {
   __shared__ float scratch[32];
   pdl_trigger();
-  pdl_wait();
   const int r = blockIdx.x;
-  const float* row = x + (size_t)(rows ? rows[r] : r) * ldx;
+  const int src = rows ? rows[r] : r;                     // (the step's metadata: readable before the wait)
+  pdl_wait();
+  const float* row = x + (size_t)src * ldx;
+  RowCache c;
+  row_load(row, dim, c);
   float mean, rstd;
-  row_stats(row, dim, kind, eps, scratch, mean, rstd);
+  row_stats(row, c, dim, kind, eps, scratch, mean, rstd);
   TO* o = out + (size_t)r * dim;
-  for (int d = threadIdx.x; d < dim; d += blockDim.x) o[d] = from_f32<TO>((row[d] - mean) * rstd * gain[d]);
+  if (c.whole) {
+#pragma unroll
+    for (int i = 0; i < NORM_CACHE; ++i) {
+      const int d = threadIdx.x + i * blockDim.x;
+      if (d < dim) o[d] = from_f32<TO>((c.v[i] - mean) * rstd * gain[d]);
+    }
+  } else {
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) o[d] = from_f32<TO>((row[d] - mean) * rstd * gain[d]);
+  }
 }
 
 __global__ void norm_add_kernel(float* x, long long ldx, const float* y, long long ldy, const float* __restrict__ gain,
@@ -49,13 +94,35 @@ __global__ void norm_add_kernel(float* x, long long ldx, const float* y, long lo
   pdl_trigger();
   pdl_wait();
   const float* row = y + (size_t)blockIdx.x * ldy;
-  float mean, rstd;
-  row_stats(row, dim, kind, eps, scratch, mean, rstd);
   float* o = x + (size_t)blockIdx.x * ldx;
-  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-    const float v = o[d] + (row[d] - mean) * rstd * gain[d];
-    o[d] = v;
-    if (copy) copy[(size_t)blockIdx.x * dim + d] = __float2bfloat16_rn(v);
+  RowCache c;
+  row_load(row, dim, c);
+  float old[NORM_CACHE];
+  if (c.whole) {                                          // the stream's own rows are requested with y's
+#pragma unroll
+    for (int i = 0; i < NORM_CACHE; ++i) {
+      const int d = threadIdx.x + i * blockDim.x;
+      old[i] = d < dim ? o[d] : 0.f;
+    }
+  }
+  float mean, rstd;
+  row_stats(row, c, dim, kind, eps, scratch, mean, rstd);
+  if (c.whole) {
+#pragma unroll
+    for (int i = 0; i < NORM_CACHE; ++i) {
+      const int d = threadIdx.x + i * blockDim.x;
+      if (d < dim) {
+        const float v = old[i] + (c.v[i] - mean) * rstd * gain[d];
+        o[d] = v;
+        if (copy) copy[(size_t)blockIdx.x * dim + d] = __float2bfloat16_rn(v);
+      }
+    }
+  } else {
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+      const float v = o[d] + (row[d] - mean) * rstd * gain[d];
+      o[d] = v;
+      if (copy) copy[(size_t)blockIdx.x * dim + d] = __float2bfloat16_rn(v);
+    }
   }
 }
 
