@@ -51,7 +51,30 @@ CFG_B = {
          "mlp": {"kind": "dense", "ff": 128, "limit": 1.0}},
     ],
 }
-CONFIGS = {"A": (CFG_A, 11), "B": (CFG_B, 12)}
+# awkward sizes: nothing is a multiple of 8 (every product runs on the 32-bit tiles, cache rows are read
+# value by value), one attention head, a window of one, every expert chosen, three groups, five taps
+CFG_C = {
+    "architecture": "Potivik", "vocab": 97, "width": 44, "norm": {"eps": 1e-5}, "logit_softcap": 4.0,
+    "token_side": {"dim": 3},
+    "layers": [
+        {"type": "latent_attention",
+         "mixer": {"heads": 1, "dim": 10, "rot_dim": 6, "vdim": 7, "kv_rank": 21, "scale": 0.4,
+                   "mask": {"size": 5}, "rot": {"base": 30.0, "dims": 2}},
+         "mlp": {"kind": "moe", "router": {"experts": 2, "top": 2}, "expert": {"ff": 9, "limit": 1.0}}},
+        {"type": "mamba2",
+         "mixer": {"heads": 3, "vdim": 5, "state": 33, "groups": 3, "conv": 5, "norm_groups": 3},
+         "mlp": {"kind": "dense", "ff": 20, "limit": 0.5}},
+        {"type": "latent_attention",
+         "mixer": {"heads": 5, "dim": 4, "rot_dim": 2, "vdim": 3, "kv_rank": 9, "scale": 0.5,
+                   "mask": {"size": 1}, "rot": {"base": 10000.0, "dims": 2}},
+         "mlp": None},
+        {"type": "mamba2",
+         "mixer": {"heads": 1, "vdim": 3, "state": 4, "groups": 1, "conv": 1, "norm_groups": 1},
+         "mlp": {"kind": "moe", "router": {"experts": 7, "top": 1}, "expert": {"ff": 64, "limit": 3.0},
+                 "shared": {"ff": 5, "limit": 3.0}}},
+    ],
+}
+CONFIGS = {"A": (CFG_A, 11), "B": (CFG_B, 12), "C": (CFG_C, 13)}
 
 
 def _bf16_exact(t: torch.Tensor) -> torch.Tensor:
