@@ -168,25 +168,29 @@ __device__ __forceinline__ void load_row_vec(const float* src, float* dst, int D
   }
 }
 
-// One block per (token, group of up to HB heads); one warp per head.  Key rows arrive in tiles of 32
-// in shared memory (32-bit), shared by the block's heads.  Lane j scores key j of the tile; the output's
-// columns are spread over the lanes (RL per lane).
-constexpr int LA_HB = 8, LA_KT = 32;
+// One block per (token, group of up to LA_HB heads, chunk of keys); a warp looks after LA_HW heads, whose
+// queries it holds in registers, the lanes over the dimensions of a cache row.  Key rows arrive in tiles
+// of LA_KT in shared memory (32-bit), shared by the block's heads.  Per key a warp reads the row ONCE
+// (conflict-free, consecutive lanes consecutive values): the same registers give the scores of its heads
+// (a product summed over the lanes) and then enter the weighted sums; the softmax is kept per key (the
+// sums are rescaled only when a score exceeds the running maximum, a branch the whole warp takes together).
+// (Measured against a variant that takes a tile's scores first, lane j keeping key j's, and then the
+// weighted sums in a second pass over the tile: 17.9 against 26.0 ms for four layers of a 2,048-token
+// prompt at 16 heads, latent 512 + 64, window 1,024.)
+constexpr int LA_HW = 2, LA_WARPS = 8, LA_HB = LA_HW * LA_WARPS, LA_KT = 32, LA_RR = 4;   // rotated part: up to 128
 
 template <typename TC, int RL>
-__global__ void latent_attention_kernel(const float* qp, const TC* pages, const int* block_table, int bt_stride,
-                                        int page_size, int n_pages, const int* tok_req, const int* tok_pos,
-                                        const float* gate, long long ld_gate, float* out, long long ldo, int H, int r,
-                                        int dr, float scale, int window, int splits, int chunk, float* ws, int* status) {
-  extern __shared__ __align__(16) float smem[];
+__global__ void __launch_bounds__(32 * LA_WARPS, 2)      // (two blocks an SM: at most 128 registers a thread)
+latent_attention_kernel(const float* qp, const TC* pages, const int* block_table, int bt_stride, int page_size,
+                        int n_pages, const int* tok_req, const int* tok_pos, const float* gate, long long ld_gate,
+                        float* out, long long ldo, int H, int r, int dr, float scale, int window, int splits, int chunk,
+                        float* ws, int* status) {
+  extern __shared__ __align__(16) float ks[];      // [LA_KT][Dk]
   pdl_trigger();
-  const int Dk = r + dr, Dp = Dk + 1;
-  float* qs = smem;                        // [LA_HB][Dk]
-  float* ks = smem + LA_HB * Dk;           // [LA_KT][Dp]
+  const int Dk = r + dr;
   const int t = blockIdx.x, h0 = blockIdx.y * LA_HB;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int h = h0 + warp;
-  const bool live = h < H;
+  const int hw = h0 + warp * LA_HW;                // this warp's first head
   const int pos = tok_pos[t];
   const int* table = block_table + (size_t)tok_req[t] * bt_stride;
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
@@ -196,25 +200,27 @@ __global__ void latent_attention_kernel(const float* qp, const TC* pages, const 
   const int k_begin = splits > 1 ? lo + (int)blockIdx.z * chunk : lo;
   const int k_end = splits > 1 ? min(pos, k_begin + chunk - 1) : pos;
   pdl_wait();
-  {
-    // this warp's query: four values are requested before any is stored (see load_row_vec)
-    const float* src = qp + ((size_t)t * H + (live ? h : 0)) * Dk;
-    float* dst = qs + warp * Dk;
-    for (int d0 = lane; d0 < Dk; d0 += 128) {
-      float v[4];
+  float ql[LA_HW][RL], qr[LA_HW][LA_RR], acc[LA_HW][RL], m[LA_HW], l[LA_HW];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) v[u] = (live && d0 + 32 * u < Dk) ? src[d0 + 32 * u] : 0.f;
+  for (int hh = 0; hh < LA_HW; ++hh) {
+    const bool live = hw + hh < H;
+    const float* src = qp + ((size_t)t * H + (live ? hw + hh : 0)) * Dk;
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (d0 + 32 * u < Dk) dst[d0 + 32 * u] = v[u];
+    for (int i = 0; i < RL; ++i) {
+      const int d = lane + 32 * i;
+      ql[hh][i] = (live && d < r) ? src[d] : 0.f;
+      acc[hh][i] = 0.f;
     }
-  }
-  float m = -INFINITY, l = 0.f, acc[RL];
 #pragma unroll
-  for (int i = 0; i < RL; ++i) acc[i] = 0.f;
-  const float* q = qs + warp * Dk;
+    for (int i = 0; i < LA_RR; ++i) {
+      const int d = lane + 32 * i;
+      qr[hh][i] = (live && d < dr) ? src[r + d] : 0.f;
+    }
+    m[hh] = -INFINITY;
+    l[hh] = 0.f;
+  }
   for (int k0 = k_begin; k0 <= k_end; k0 += LA_KT) {
-    __syncthreads();                       // the last tile has been used (and q is in place)
+    __syncthreads();                       // the last tile has been used
     {
       // eight threads share a key row; its page is looked up once
       const int j = threadIdx.x >> 3, sub = threadIdx.x & 7;
@@ -228,7 +234,7 @@ __global__ void latent_attention_kernel(const float* qp, const TC* pages, const 
           src = pages + ((size_t)page * page_size + kp % page_size) * Dk;
         }
       }
-      float* dst = ks + j * Dp;
+      float* dst = ks + j * Dk;
       if (src == nullptr) {
         for (int d = sub; d < Dk; d += 8) dst[d] = 0.f;
       } else if (vec) {
@@ -238,59 +244,72 @@ __global__ void latent_attention_kernel(const float* qp, const TC* pages, const 
       }
     }
     __syncthreads();
-    if (!live) continue;
-    float s = -INFINITY;
-    if (k0 + lane <= k_end) {
-      const float* kr = ks + lane * Dp;
-      // four partial sums, so that the additions do not wait for one another; added in a fixed order
-      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-      int d = 0;
-      for (; d + 4 <= Dk; d += 4) {
-        d0 = fmaf(q[d], kr[d], d0);
-        d1 = fmaf(q[d + 1], kr[d + 1], d1);
-        d2 = fmaf(q[d + 2], kr[d + 2], d2);
-        d3 = fmaf(q[d + 3], kr[d + 3], d3);
-      }
-      for (; d < Dk; ++d) d0 = fmaf(q[d], kr[d], d0);
-      s = ((d0 + d1) + (d2 + d3)) * scale;
-    }
-    const float m_new = fmaxf(m, warp_max(s));
-    const float corr = expf(m - m_new);    // (0 on the first tile: m = -inf)
-    const float p = k0 + lane <= k_end ? expf(s - m_new) : 0.f;
-    l = l * corr + warp_sum(p);
-    m = m_new;
-#pragma unroll
-    for (int i = 0; i < RL; ++i) acc[i] *= corr;
+    if (hw >= H) continue;
     const int n_keys = min(LA_KT, k_end - k0 + 1);
     for (int j = 0; j < n_keys; ++j) {
-      const float pj = __shfl_sync(0xffffffffu, p, j);
-      const float* kr = ks + j * Dp;
+      const float* row = ks + j * Dk;
+      float kl[RL], kr[LA_RR];
 #pragma unroll
       for (int i = 0; i < RL; ++i) {
         const int d = lane + 32 * i;
-        if (d < r) acc[i] = fmaf(pj, kr[d], acc[i]);
+        kl[i] = d < r ? row[d] : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < LA_RR; ++i) {
+        const int d = lane + 32 * i;
+        kr[i] = d < dr ? row[r + d] : 0.f;
+      }
+#pragma unroll
+      for (int hh = 0; hh < LA_HW; ++hh) {
+        float p0 = 0.f, p1 = 0.f;                          // two chains; added in a fixed order
+#pragma unroll
+        for (int i = 0; i < RL; ++i) {
+          if (i & 1) p1 = fmaf(ql[hh][i], kl[i], p1);
+          else p0 = fmaf(ql[hh][i], kl[i], p0);
+        }
+#pragma unroll
+        for (int i = 0; i < LA_RR; ++i) {
+          if (i & 1) p1 = fmaf(qr[hh][i], kr[i], p1);
+          else p0 = fmaf(qr[hh][i], kr[i], p0);
+        }
+        const float sc = warp_sum(p0 + p1) * scale;       // every lane gets the same sum
+        if (sc > m[hh]) {                                  // (the whole warp together)
+          const float corr = expf(m[hh] - sc);             // 0 for the first key: m = -inf
+          l[hh] *= corr;
+#pragma unroll
+          for (int i = 0; i < RL; ++i) acc[hh][i] *= corr;
+          m[hh] = sc;
+        }
+        const float p = expf(sc - m[hh]);
+        l[hh] += p;
+#pragma unroll
+        for (int i = 0; i < RL; ++i) acc[hh][i] = fmaf(p, kl[i], acc[hh][i]);
       }
     }
   }
-  if (!live) return;
-  if (splits > 1) {
-    // partial result of this chunk: running maximum, sum of weights, weighted sum (not yet divided)
-    float* w = ws + (((size_t)t * H + h) * splits + blockIdx.z) * (r + 2);
-    if (lane == 0) { w[0] = m; w[1] = l; }
+#pragma unroll
+  for (int hh = 0; hh < LA_HW; ++hh) {
+    const int h = hw + hh;
+    if (h >= H) continue;
+    if (splits > 1) {
+      // partial result of this chunk: running maximum, sum of weights, weighted sum (not yet divided)
+      float* w = ws + (((size_t)t * H + h) * splits + blockIdx.z) * (r + 2);
+      if (lane == 0) { w[0] = m[hh]; w[1] = l[hh]; }
+#pragma unroll
+      for (int i = 0; i < RL; ++i) {
+        const int d = lane + 32 * i;
+        if (d < r) w[2 + d] = acc[hh][i];
+      }
+      continue;
+    }
+    const float g = gate ? hy_sigmoid(gate[(size_t)t * ld_gate + h]) : 1.f;
+    const float inv = g / l[hh];
+    float* o = out + (size_t)t * ldo + (size_t)h * r;
 #pragma unroll
     for (int i = 0; i < RL; ++i) {
       const int d = lane + 32 * i;
-      if (d < r) w[2 + d] = acc[i];
+      if (d < r) o[d] = acc[hh][i] * inv;
     }
-    return;
-  }
-  const float g = gate ? hy_sigmoid(gate[(size_t)t * ld_gate + h]) : 1.f;
-  const float inv = g / l;
-  float* o = out + (size_t)t * ldo + (size_t)h * r;
-#pragma unroll
-  for (int i = 0; i < RL; ++i) {
-    const int d = lane + 32 * i;
-    if (d < r) o[d] = acc[i] * inv;
   }
 }
 
@@ -304,21 +323,41 @@ __global__ void latent_attention_merge_kernel(const float* ws, int splits, const
   if (idx >= (long long)n * H) return;
   const int t = (int)(idx / H), h = (int)(idx - (long long)t * H);
   const float* w = ws + (size_t)idx * splits * (r + 2);
+  // the chunks' weights exp(m_s - M) once (lane s for chunk s, 32 chunks at a time), then the columns
   float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, w[(size_t)s * (r + 2)]);
+  for (int s = lane; s < splits; s += 32) M = fmaxf(M, w[(size_t)s * (r + 2)]);
+  M = warp_max(M);
   float L = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float m = w[(size_t)s * (r + 2)];
-    if (m > -INFINITY) L += expf(m - M) * w[(size_t)s * (r + 2) + 1];
+  for (int s0 = 0; s0 < splits; s0 += 32) {                // in chunk order
+    const int s = s0 + lane;
+    const float m = s < splits ? w[(size_t)s * (r + 2)] : -INFINITY;
+    const float e = m > -INFINITY ? expf(m - M) : 0.f;
+    const float el = s < splits ? e * w[(size_t)s * (r + 2) + 1] : 0.f;
+    for (int u = 0; u < 32 && s0 + u < splits; ++u) L += __shfl_sync(0xffffffffu, el, u);
   }
   const float g = gate ? hy_sigmoid(gate[(size_t)t * ld_gate + h]) : 1.f;
-  for (int d = lane; d < r; d += 32) {
-    float a = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float m = w[(size_t)s * (r + 2)];
-      if (m > -INFINITY) a += expf(m - M) * w[(size_t)s * (r + 2) + 2 + d];
+  const float inv = g / L;
+  for (int d0 = 0; d0 < r; d0 += 128) {                    // four columns per lane at a time
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int s0 = 0; s0 < splits; s0 += 32) {
+      const int s = s0 + lane;
+      const float m = s < splits ? w[(size_t)s * (r + 2)] : -INFINITY;
+      const float e = m > -INFINITY ? expf(m - M) : 0.f;
+      for (int u = 0; u < 32 && s0 + u < splits; ++u) {
+        const float eu = __shfl_sync(0xffffffffu, e, u);
+        const float* wu = w + (size_t)(s0 + u) * (r + 2) + 2;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const int d = d0 + lane + 32 * v;
+          if (d < r) a[v] = fmaf(eu, wu[d], a[v]);
+        }
+      }
     }
-    out[(size_t)t * ldo + (size_t)h * r + d] = a * (g / L);
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int d = d0 + lane + 32 * v;
+      if (d < r) out[(size_t)t * ldo + (size_t)h * r + d] = a[v] * inv;
+    }
   }
 }
 
@@ -330,15 +369,15 @@ __global__ void latent_attention_merge_kernel(const float* ws, int splits, const
 // the contexts' lengths; chunks lie at fixed distances from the first visible key, so a chunk's partial
 // result does not depend on how many chunks there are.
 GB_API int gb_latent_attention_chunks(int n, int H, int window, int max_ctx, int* chunk_out) {
-  const int blocks = n * gb_div_up(H, 8);
+  const int blocks = n * gb_div_up(H, LA_HB);
   int wanted = 592 / (blocks > 0 ? blocks : 1);
   if (wanted > 64) wanted = 64;
   const int span = window > 0 ? window : (max_ctx > 0 ? max_ctx : 1);
-  if (wanted <= 1 || span <= 64) { *chunk_out = span; return 1; }
+  if (wanted <= 1 || span <= 32) { *chunk_out = span; return 1; }
   int chunk;
   if (window > 0) {
     chunk = 32 * gb_div_up(gb_div_up(span, wanted), 32);
-    if (chunk < 64) chunk = 64;
+    if (chunk < 32) chunk = 32;
   } else {
     chunk = 256;
     while (gb_div_up(span, chunk) > 2 * wanted) chunk *= 2;
@@ -347,7 +386,7 @@ GB_API int gb_latent_attention_chunks(int n, int H, int window, int max_ctx, int
   return gb_div_up(span, chunk);
 }
 // Rows of (latent size + 2) floats a launch's partial results may need, whatever its sizes.
-GB_API int gb_latent_attention_workspace_rows() { return 8 * 2 * (592 + 592); }
+GB_API int gb_latent_attention_workspace_rows() { return LA_HB * 2 * (592 + 592); }
 
 // a0 fused rows [q heads (plain | rotated) | ... ] (f32), a1 their stride, a2 column of [latent | rotated key],
 // a3 gain of the latent's norm [r], a4 inv_freq [rot_dims / 2], a5 rot_dims, a6 token -> request, a7 token ->
@@ -403,12 +442,13 @@ GB_OP(gb_op_latent_attention) {
   if (n <= 0) return 0;
   if (r > 512) GB_FAIL(GB_ERR_ARG, "latent_attention: latent size %d (at most 512)", r);
   const int Dk = r + dr;
-  const size_t smem = sizeof(float) * ((size_t)LA_HB * Dk + (size_t)LA_KT * (Dk + 1));
+  if (dr > 32 * LA_RR) GB_FAIL(GB_ERR_ARG, "latent_attention: rotated size %d (at most %d)", dr, 32 * LA_RR);
+  const size_t smem = sizeof(float) * (size_t)LA_KT * Dk;
   int chunk = 0;
   int splits = gb_latent_attention_chunks(n, H, (int)a[17], (int)a[18], &chunk);
   float* ws = op_ptr<float>(a[19]);
   if (ws == nullptr || (long long)n * H * splits > gb_latent_attention_workspace_rows()) splits = 1;
-  const dim3 grid(n, gb_div_up(H, LA_HB), splits), block(32 * LA_HB);
+  const dim3 grid(n, gb_div_up(H, LA_HB), splits), block(32 * LA_WARPS);
 #define LA(TC, RL)                                                                                                   \
   do {                                                                                                               \
     static size_t allowed = 48 * 1024;     /* raised once per size, before any stream capture replays the launch */ \
