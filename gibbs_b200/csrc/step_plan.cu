@@ -36,6 +36,8 @@ typedef int (*LinearSimtFn)(const void*, int, long long, const void*, int, long 
                             long long, int, int, int, int, cudaStream_t);
 typedef int (*LinearTcFn)(const void*, long long, const void*, long long, const float*, void*, int, long long, int, int,
                           int, float*, int, int, int*, cudaStream_t);
+typedef int (*LinearTcGluFn)(const void*, long long, const void*, long long, const float*, void*, int, long long, int, int,
+                             int, float*, int, int, int*, cudaStream_t, float, float, float);
 typedef int (*LinearTcSplitsFn)(int, int, int);
 typedef int (*ShortConvFn)(const void*, int, long long, const float*, const float*, float*, long long, const int*,
                            const int*, const int*, const int*, void*, int, int, int, int, int, cudaStream_t);
@@ -69,9 +71,10 @@ typedef int (*AddPendingFn)(float*, long long, const float*, int, const float*, 
 enum Fn : int { F_EMBED = 0, F_RMSNORM, F_LINEAR_SIMT, F_LINEAR_TC, F_LINEAR_TC_SPLITS, F_SHORT_CONV,
                 F_SHORT_CONV_PARTIALS, F_QKROPE, F_QKROPE_PARTIALS, F_PAGED_ATTENTION, F_ATTENTION_TC,
                 F_ATTENTION_TCGEN05, F_ATTENTION_TCGEN05_SUPPORTED, F_SWIGLU, F_LINEAR_DECODE, F_LINEAR_DECODE_PARTS,
-                F_LINEAR_DECODE_SUPPORTED, F_ADD_PENDING, F_LINEAR_DECODE_NORMED_OK, F_SCALE_SOFTCAP, F_COUNT };
+                F_LINEAR_DECODE_SUPPORTED, F_ADD_PENDING, F_LINEAR_DECODE_NORMED_OK, F_SCALE_SOFTCAP, F_LINEAR_TC_GLU,
+                F_COUNT };
 // which library an entry point belongs to (0: core, 1: tensor cores), for the caller to fetch the message
-const int FN_LIB[F_COUNT] = {0, 0, 0, 1, 1, 0, 0, 0, 0, 0, 1, 1, 1, 0, 1, 1, 1, 0, 1, 0};
+const int FN_LIB[F_COUNT] = {0, 0, 0, 1, 1, 0, 0, 0, 0, 0, 1, 1, 1, 0, 1, 1, 1, 0, 1, 0, 1};
 void* g_fn[F_COUNT];
 
 enum Op : int { P_EMBED = 1, P_RMSNORM = 2, P_LINEAR = 3, P_SHORT_CONV = 4, P_QKROPE = 5, P_ATTENTION = 6, P_SWIGLU = 7,
@@ -185,13 +188,15 @@ int run_op(Walk& w, const PlanOp& o, bool force = false) {
     case P_LINEAR: {
       // a0 x, a1 its row stride, a2 W, a3 its row stride, a4 bias, a5 out, a6 its row stride, a7 rows (N or W, a
       // symbol), a8 n, a9 k, a10 kernel (0 tensor cores, 1 FFMA), a11 mode (0 bf16, 1 f32, 2 add into f32, 3 SwiGLU),
-      // a12 x dtype, a13 W dtype, a14 out dtype
+      // a12 x dtype, a13 W dtype, a14 out dtype; mode 3 with f0 != 0: the gated unit's constants f0 alpha, f1 limit
+      // (0: none), f2 what is added to u (all zero: SwiGLU)
+      const bool glu = a[11] == 3 && o.f[0] != 0.0;
       const int M = (int)val(w, a[7]);
       if (M <= 0) return 0;
       const float* bias = ptr<const float>(w, a[4]);
       const PlanOp* lazy = (o.flags & LF_NORMED) ? w.lazy_norm : nullptr;
       w.lazy_norm = nullptr;
-      if (a[10] == 0 && M <= w.decode_products &&
+      if (a[10] == 0 && !glu && M <= w.decode_products &&
           ((LinearDecodeSupportedFn)g_fn[F_LINEAR_DECODE_SUPPORTED])(M, ptr<const void>(w, a[2]), a[3], (int)a[9])) {
         // up to 64 rows: K is split inside a cluster, and a norm that was left out runs inside the product
         const int n = (int)a[8], k = (int)a[9];
@@ -235,6 +240,12 @@ int run_op(Walk& w, const PlanOp& o, bool force = false) {
         // a large unsplit product into the residual stream is deferred as a whole (ops.DEFER_WHOLE_ROWS)
         const bool whole = (o.flags & LF_RESIDUAL) && splits == 1 && M >= w.defer_whole_rows;
         const bool defer = (wants && splits > 1 && (a[11] == 0 || a[11] == 2)) || whole;
+        if (glu)
+          PLAN_CALL(w, F_LINEAR_TC_GLU, ((LinearTcGluFn)g_fn[F_LINEAR_TC_GLU])(
+              ptr<const void>(w, a[0]), a[1], ptr<const void>(w, a[2]), a[3], bias, ptr<void>(w, a[5]), (int)a[11], a[6],
+              M, n, k, splits > 1 ? w.ws : nullptr, 0, w.tc_flags, w.status, w.stream, (float)o.f[0], (float)o.f[1],
+              (float)o.f[2]));
+        else
         PLAN_CALL(w, F_LINEAR_TC, ((LinearTcFn)g_fn[F_LINEAR_TC])(
             ptr<const void>(w, a[0]), a[1], ptr<const void>(w, a[2]), a[3], bias, ptr<void>(w, a[5]), (int)a[11], a[6],
             M, n, k, (splits > 1 || whole) ? w.ws : nullptr, whole ? 2 : (defer ? 1 : 0), w.tc_flags, w.status,

@@ -51,7 +51,8 @@ _FUNCTIONS = [("core", "gb_embed"), ("core", "gb_rmsnorm"), ("core", "gb_linear_
               ("tensorcore", "gb_attention_tcgen05_supported"), ("core", "gb_swiglu"),
               ("tensorcore", "gb_linear_decode"), ("tensorcore", "gb_linear_decode_parts"),
               ("tensorcore", "gb_linear_decode_supported"), ("core", "gb_add_pending"),
-              ("tensorcore", "gb_linear_decode_normed_ok"), ("core", "gb_scale_softcap")]
+              ("tensorcore", "gb_linear_decode_normed_ok"), ("core", "gb_scale_softcap"),
+              ("tensorcore", "gb_linear_tc_glu")]
 
 
 def register_op(name: str, function) -> int:
@@ -171,11 +172,13 @@ class PlanBuilder:
         return out
 
     def linear(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out, mode: str,
-               rows_symbol: int = S_N, partials: str = "", role: str = "") -> torch.Tensor:
+               rows_symbol: int = S_N, partials: str = "", role: str = "", glu=None) -> torch.Tensor:
         """out (+)= x W^T + b.  mode: 'plain' (out in its own dtype), 'residual' (adds into the
         float32 residual; partial sums may be left to the next norm) or 'swiglu'.  ``partials``:
         '' | 'one_each' | 'always': when K is split, leave the partial tiles to the next
-        operation (a short convolution or q/k kernel that adds them itself)."""
+        operation (a short convolution or q/k kernel that adds them itself).  ``glu`` (mode
+        'swiglu'): (alpha, limit, add) of the gated unit g' sigmoid(alpha g') (u' + add) with
+        g' = min(g, limit), u' = clamp(u, -limit, limit); limit 0: none.  None: SwiGLU."""
         n, k = weight.shape
         if x.shape[1] != k or weight.stride(1) != 1 or x.stride(1) != 1:
             raise NotPlannable("a product's operands have contiguous rows of equal length")
@@ -221,8 +224,8 @@ class PlanBuilder:
                              out if isinstance(out, int) else out.data_ptr(),
                              n if isinstance(out, int) else out.stride(0), sym(rows_symbol), n, k, 0 if use_tc else 1,
                              code, ops.dtype_code(x.dtype), ops.dtype_code(weight.dtype),
-                             ops.F32 if isinstance(out, int) else ops.dtype_code(out.dtype)], flags=flags,
-                  label="linear:" + (role or mode))
+                             ops.F32 if isinstance(out, int) else ops.dtype_code(out.dtype)],
+                  [] if glu is None else [float(v) for v in glu], flags=flags, label="linear:" + (role or mode))
         return out
 
     def short_conv(self, bcx: torch.Tensor, taps: torch.Tensor, bias, slot_view, hidden: int, kernel: int):

@@ -267,14 +267,16 @@ DEFER_WHOLE_ROWS = 256
 
 
 def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-              accumulate: bool = False, swiglu: bool = False, defer: bool = False):
+              accumulate: bool = False, swiglu: bool = False, defer: bool = False, glu=None):
     """out (+)= a @ w.T (+ bias) for bfloat16 a and w on the tensor cores
     (csrc/gemm_tc.cu).  ``swiglu``: w holds gate and up rows alternating in
     blocks of 64 and out [m, n/2] gets (g * sigmoid(g)) * u.
     ``defer`` (with ``accumulate``, or for a plain bfloat16 product): when
     the kernel splits K, nothing is written to ``out``; the partial sums
     [splits, m, n] are returned instead, for the caller's next kernel to add
-    (without the bias).  Otherwise returns ``out``."""
+    (without the bias).  Otherwise returns ``out``.
+    ``glu`` (with ``swiglu``): (alpha, limit, add) of the gated unit g' sigmoid(alpha g') (u' + add)
+    with g' = min(g, limit), u' = clamp(u, -limit, limit); limit 0: none."""
     # (this wrapper runs some seventy times a step: its checks are the cheap ones)
     lib = _LIBS.get("tensorcore") or _lib("tensorcore")
     m, k = a.shape
@@ -314,14 +316,15 @@ def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     whole = bool(defer and accumulate and splits == 1 and m >= DEFER_WHOLE_ROWS)
     ws = torch.empty((splits, m, n), dtype=torch.float32, device=a.device) if (splits > 1 or whole) else None
     defer = bool(defer and (accumulate or mode == 0) and splits > 1) or whole
-    rc = lib.gb_linear_tc(
+    extra = () if glu is None else tuple(_c_float(float(v)) for v in glu)
+    rc = (lib.gb_linear_tc if glu is None else lib.gb_linear_tc_glu)(
         _c_void(a.data_ptr()), _c_ll(a.stride(0) if m > 1 else max(a.stride(0), k)), _c_void(w.data_ptr()),
         _c_ll(w.stride(0) if n > 1 else max(w.stride(0), k)), _NULL if bias is None else _c_void(bias.data_ptr()),
         _c_void(out.data_ptr()), _c_int(mode), _c_ll(out.stride(0) if m > 1 else max(out.stride(0), n_out)), _c_int(m),
         _c_int(n), _c_int(k), _NULL if ws is None else _c_void(ws.data_ptr()),
         _c_int(2) if whole else (_ONE if defer else _ZERO),
         _c_int(_TC_FLAGS),
-        _status_ptr(a), _STREAM if _STREAM is not None else _stream())
+        _status_ptr(a), _STREAM if _STREAM is not None else _stream(), *extra)
     if rc < 0:
         check(lib, rc)
     _launched(rc)

@@ -24,7 +24,7 @@ from .. import ops
 from ..ops import hybrid
 from ..ops.library import library
 from .base import FeedForward, TensorDecl, VECTOR, register_part, tensor_bytes
-from .linear import interleave_gate_up
+from .linear import can_fuse_swiglu, interleave_gate_up
 from .runner import BranchPart, Runner, keep
 
 
@@ -41,18 +41,24 @@ class ClampedGLU(BranchPart, FeedForward):
         self.alpha, self.up_add = float(params.get("alpha", 1.702)), float(params.get("up_add", 1.0))
         if tensors["gate"].dtype != tensors["up"].dtype:
             raise ValueError("gate and up projections are stored in different dtypes")
-        self.gate_up = torch.cat([tensors["gate"], tensors["up"]], 0).contiguous()
+        # in bfloat16 gate and up are one product whose epilogue applies the unit (as SwiGLU's does)
+        self.fused = can_fuse_swiglu(tensors["gate"], rt)
+        join = interleave_gate_up if self.fused else (lambda g, u: torch.cat([g, u], 0))
+        self.gate_up = join(tensors["gate"], tensors["up"]).contiguous()
         self.down = tensors["down"].contiguous()
 
     def kernel_libraries(self):
         return tuple(set(ops.linear_libraries(self.gate_up.dtype, self.rt.dtype)) | {"core", hybrid.LIBRARY})
 
     def run(self, rn: Runner, h, out, caches=None):
-        gu = rn.buffer("glu_gate_up", 2 * self.inner, torch.float32)
-        rn.linear(h, self.gate_up, None, gu, role="glu_gate_up")
         act = rn.buffer("glu_act", self.inner)
-        rn.op("clamped_glu", [gu.data_ptr(), gu.stride(0), act.data_ptr(), ops.dtype_code(act.dtype), act.stride(0),
-                              rn.N, self.inner], [self.alpha, self.limit, self.up_add])
+        if self.fused:
+            rn.glu_linear(h, self.gate_up, act, (self.alpha, self.limit, self.up_add), role="glu_gate_up")
+        else:
+            gu = rn.buffer("glu_gate_up", 2 * self.inner, torch.float32)
+            rn.linear(h, self.gate_up, None, gu, role="glu_gate_up")
+            rn.op("clamped_glu", [gu.data_ptr(), gu.stride(0), act.data_ptr(), ops.dtype_code(act.dtype), act.stride(0),
+                                  rn.N, self.inner], [self.alpha, self.limit, self.up_add])
         rn.linear(act, self.down, None, out, role="glu_down")
 
 

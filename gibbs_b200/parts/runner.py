@@ -34,6 +34,11 @@ class Runner:
         the product in the timing table."""
         raise NotImplementedError
 
+    def glu_linear(self, x, weight, out, glu, role: str = "") -> None:
+        """out = unit(x weight^T) on the tensor cores, for a weight whose gate and up rows alternate in
+        blocks of 64 (``parts.linear.interleave_gate_up``); ``glu`` = (alpha, limit, add)."""
+        raise NotImplementedError
+
     def op(self, name: str, a, f=(), label: str = "") -> None:
         raise NotImplementedError
 
@@ -60,6 +65,9 @@ class Eager(Runner):
 
     def linear(self, x, weight, bias, out, role=""):
         ops.linear(x[:self.N] if x.shape[0] != self.N else x, weight, bias, out)
+
+    def glu_linear(self, x, weight, out, glu, role=""):
+        ops.linear_tc(x[:self.N] if x.shape[0] != self.N else x, weight, None, out, swiglu=True, glu=glu)
 
     def op(self, name, a, f=(), label=""):
         hybrid.call(name, a, f, device=self.rt.device)
@@ -89,6 +97,9 @@ class Planned(Runner):
 
     def linear(self, x, weight, bias, out, role=""):
         self.plan.linear(x, weight, bias, out, "plain", role=role or "plain")
+
+    def glu_linear(self, x, weight, out, glu, role=""):
+        self.plan.linear(x, weight, None, out, "swiglu", role=role or "glu", glu=glu)
 
     def op(self, name, a, f=(), label=""):
         self.plan.emit(hybrid.plan_id(name), list(a), list(f), label=label or name)

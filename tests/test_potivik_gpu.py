@@ -77,9 +77,10 @@ def test_norm_in_front_and_behind(kind, ref, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_clamped_unit_alone(dtype):
+@pytest.mark.parametrize("f", [40, 128])      # 128: in bfloat16 the unit runs in the epilogue of the gate/up product
+def test_clamped_unit_alone(dtype, f):
     g = gen(2)
-    d, f, limit = 64, 40, 0.7
+    d, limit = 64, 0.7
     W = {k: bf(torch.randn(*s, generator=g) * 0.3) for k, s in (("gate", (f, d)), ("up", (f, d)), ("down", (d, f)))}
     part = make_part("feed_forward", "clamped_glu", {"hidden": d, "inner": f, "limit": limit}, W, DTYPES[dtype])
     h = bf(torch.randn(50, d, generator=g) * 2)               # many pre-activations beyond the clamps, on both sides
