@@ -223,7 +223,8 @@ latent_attention_kernel(const float* qp, const TC* pages, const int* block_table
     __syncthreads();                       // the last tile has been used
     {
       // eight threads share a key row; its page is looked up once
-      const int j = threadIdx.x >> 3, sub = threadIdx.x & 7;
+      const int sub = threadIdx.x & 7;
+      for (int j = threadIdx.x >> 3; j < LA_KT; j += blockDim.x >> 3) {
       const int kp = k0 + j;
       const TC* src = nullptr;
       if (kp <= k_end) {
@@ -241,6 +242,7 @@ latent_attention_kernel(const float* qp, const TC* pages, const int* block_table
         load_row_vec(src, dst, Dk, sub);
       } else {
         for (int d = sub; d < Dk; d += 8) dst[d] = to_f32(src[d]);
+      }
       }
     }
     __syncthreads();
@@ -448,7 +450,9 @@ GB_OP(gb_op_latent_attention) {
   int splits = gb_latent_attention_chunks(n, H, (int)a[17], (int)a[18], &chunk);
   float* ws = op_ptr<float>(a[19]);
   if (ws == nullptr || (long long)n * H * splits > gb_latent_attention_workspace_rows()) splits = 1;
-  const dim3 grid(n, gb_div_up(H, LA_HB), splits), block(32 * LA_WARPS);
+  // (fewer heads than a block has room for: fewer warps, so that none idles through the key tiles)
+  const int warps = H >= LA_HB ? LA_WARPS : (gb_div_up(H, LA_HW) < 2 ? 2 : gb_div_up(H, LA_HW));
+  const dim3 grid(n, gb_div_up(H, LA_HB), splits), block(32 * warps);
 #define LA(TC, RL)                                                                                                   \
   do {                                                                                                               \
     static size_t allowed = 48 * 1024;     /* raised once per size, before any stream capture replays the launch */ \
