@@ -10,7 +10,9 @@
 //                             y_t = S^T C_t + D[h] * x_t
 //                           Everything here is 32-bit.
 //
-// State layout in a slot: conv [K-1][channels] (oldest first); recurrence [heads][head_dim][state].
+// State layout in a slot: conv [K-1][channels] (oldest first); recurrence [heads][head_dim][state], or
+// [heads][state][head_dim] where the column-per-thread kernel runs (which kernel runs depends on the layer's
+// sizes only, so a layer's state always has one layout).
 #include "hybrid.cuh"
 
 namespace {
@@ -156,6 +158,129 @@ __global__ void ssm_scan_kernel(const float* xbc, long long ld, const float* dt_
     }
 }
 
+// The same recurrence with the state in registers and (almost) no exchange between lanes: SPLIT neighbouring
+// lanes share a column p of a head, each with 32 of the column's state values (N up to 32 * SPLIT), so a token
+// costs a thread 64 multiply-adds and the column log2(SPLIT) shuffles; B_t and C_t are read from shared memory
+// four values an instruction.  The inputs of SCOL_TOKENS tokens at a time arrive by asynchronous copies into
+// one of two buffers while the tokens of the other are consumed.
+constexpr int SCOL_TOKENS = 16, SCOL_THREADS = 64;
+
+__device__ __forceinline__ void scol_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int LEFT> __device__ __forceinline__ void scol_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(LEFT) : "memory");
+}
+
+template <int SPLIT>
+__global__ void ssm_scan_cols_kernel(const float* xbc, long long ld, const float* dt_raw, long long ld_dt,
+                                     const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                                     const float* __restrict__ dskip, float* state, long long slot_stride,
+                                     const int* slot_ids, const int* q_start, const int* q_len, float* y, long long ldy,
+                                     int H, int P, int N, int G) {
+  constexpr int NR = 32 * SPLIT, COLS = SCOL_THREADS / SPLIT;
+  extern __shared__ __align__(16) float scol[];
+  constexpr int PER = SCOL_TOKENS * (2 * NR + COLS);      // one buffer: B [T][NR] | C [T][NR] | x [T][COLS]
+  float* sRaw = scol + 2 * PER;                            // [2][T] dt before the bias
+  float* sDt = sRaw + 2 * SCOL_TOKENS;                     // [T] step size, [T] decay
+  float* sDecay = sDt + SCOL_TOKENS;
+  pdl_trigger();
+  const int col = threadIdx.x / SPLIT, q = threadIdx.x % SPLIT;
+  const int r = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * COLS, p = p0 + col;
+  const bool active = p < P;
+  const int g = h / (H / G);
+  const int inner = H * P;
+  const float bias = dt_bias[h], neg_a = -expf(a_log[h]), dsk = dskip[h];
+  const int first = q_start[r], len = q_len[r];
+  // (this kernel keeps a head's state as [state][head_dim], so that neighbouring columns lie side by side)
+  float* S = state + (size_t)slot_ids[r] * slot_stride + (size_t)h * P * N + (active ? p : 0);
+  if (N < NR)                                              // the padding N .. NR of B and C stays zero
+    for (int i = threadIdx.x; i < 2 * PER; i += blockDim.x) scol[i] = 0.f;
+  pdl_wait();
+  // this thread's state values: n = 4 (q + SPLIT i) + e, i < 8, e < 4
+  float s[32];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int n = 4 * (q + SPLIT * i) + e;
+      s[4 * i + e] = (active && n < N) ? S[(size_t)n * P] : 0.f;
+    }
+  __syncthreads();
+
+  const int pieces = N >> 2, xpieces = min(COLS, P - p0) >> 2;
+  auto stage = [&](int t0, int b) {
+    const int nt = min(SCOL_TOKENS, len - t0);
+    float* B = scol + b * PER;
+    float* C = B + SCOL_TOKENS * NR;
+    float* X = C + SCOL_TOKENS * NR;
+    for (int i = threadIdx.x; i < 2 * nt * pieces; i += blockDim.x) {
+      const int which = i / (nt * pieces), rem = i - which * nt * pieces;
+      const int tt = rem / pieces, c4 = rem - tt * pieces;
+      const float* src = xbc + (size_t)(first + t0 + tt) * ld + inner + (which ? G + g : g) * N + 4 * c4;
+      gb_cp_async_16((which ? C : B) + tt * NR + 4 * c4, src);
+    }
+    for (int i = threadIdx.x; i < nt * xpieces; i += blockDim.x) {
+      const int tt = i / xpieces, c4 = i - tt * xpieces;
+      gb_cp_async_16(X + tt * COLS + 4 * c4, xbc + (size_t)(first + t0 + tt) * ld + h * P + p0 + 4 * c4);
+    }
+    if ((int)threadIdx.x < nt)
+      gb_cp_async_4(sRaw + b * SCOL_TOKENS + threadIdx.x, dt_raw + (size_t)(first + t0 + threadIdx.x) * ld_dt + h);
+    scol_commit();
+  };
+
+  if (len > 0) stage(0, 0);
+  int b = 0;
+  for (int t0 = 0; t0 < len; t0 += SCOL_TOKENS, b ^= 1) {
+    const int nt = min(SCOL_TOKENS, len - t0);
+    if (t0 + SCOL_TOKENS < len) {
+      stage(t0 + SCOL_TOKENS, b ^ 1);
+      scol_wait<1>();                                      // this chunk has landed, the next is on its way
+    } else {
+      scol_wait<0>();
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < nt) {
+      const float dt = hy_softplus(sRaw[b * SCOL_TOKENS + threadIdx.x] + bias);
+      sDt[threadIdx.x] = dt;
+      sDecay[threadIdx.x] = expf(neg_a * dt);
+    }
+    __syncthreads();
+    const float* B = scol + b * PER;
+    const float* C = B + SCOL_TOKENS * NR;
+    const float* X = C + SCOL_TOKENS * NR;
+    for (int tt = 0; tt < nt; ++tt) {                      // (every lane, also of a column beyond P: the shuffles below)
+      const float decay = sDecay[tt], xv = active ? X[tt * COLS + col] : 0.f, dx = sDt[tt] * xv;
+      float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;        // four chains; added in a fixed order
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 b4 = *reinterpret_cast<const float4*>(B + tt * NR + 4 * (q + SPLIT * i));
+        const float4 c4 = *reinterpret_cast<const float4*>(C + tt * NR + 4 * (q + SPLIT * i));
+        s[4 * i] = fmaf(decay, s[4 * i], b4.x * dx);
+        y0 = fmaf(s[4 * i], c4.x, y0);
+        s[4 * i + 1] = fmaf(decay, s[4 * i + 1], b4.y * dx);
+        y1 = fmaf(s[4 * i + 1], c4.y, y1);
+        s[4 * i + 2] = fmaf(decay, s[4 * i + 2], b4.z * dx);
+        y2 = fmaf(s[4 * i + 2], c4.z, y2);
+        s[4 * i + 3] = fmaf(decay, s[4 * i + 3], b4.w * dx);
+        y3 = fmaf(s[4 * i + 3], c4.w, y3);
+      }
+      float ys = (y0 + y1) + (y2 + y3);
+#pragma unroll
+      for (int o = 1; o < SPLIT; o <<= 1) ys += __shfl_xor_sync(0xffffffffu, ys, o);
+      if (active && q == 0) y[(size_t)(first + t0 + tt) * ldy + h * P + p] = ys + dsk * xv;
+    }
+    __syncthreads();                                       // before the copies of the chunk after next land here
+  }
+  if (active) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int n = 4 * (q + SPLIT * i) + e;
+        if (n < N) S[(size_t)n * P] = s[4 * i + e];
+      }
+  }
+}
+
 }  // namespace
 
 // a0 in (f32; the convolved columns of a wider row), a1 its row stride, a2 taps [C, K], a3 bias [C] or 0, a4 conv
@@ -187,6 +312,22 @@ GB_OP(gb_op_ssm_scan) {
   if (R <= 0) return 0;
   if (G <= 0 || H % G) GB_FAIL(GB_ERR_ARG, "ssm_scan: %d heads in %d groups", H, G);
   if (N > 256) GB_FAIL(GB_ERR_ARG, "ssm_scan: state size %d (at most 256)", N);
+  // states of up to 128 values whose rows can be copied in 16-byte pieces: state in registers, 32 values a thread
+  if (N <= 128 && N % 4 == 0 && P % 4 == 0 && a[1] % 4 == 0 && (a[0] & 15) == 0) {
+    const int split = N <= 32 ? 1 : (N <= 64 ? 2 : 4);
+    const int cols = SCOL_THREADS / split;
+    const size_t smem_cols = sizeof(float) * (2 * (size_t)SCOL_TOKENS * (2 * 32 * split + cols) + 4 * SCOL_TOKENS);
+    const dim3 grid_cols(R, H, gb_div_up(P, cols));
+#define SCOL_LAUNCH(SP)                                                                                               \
+    gb_launch(ssm_scan_cols_kernel<SP>, grid_cols, dim3(SCOL_THREADS), smem_cols, ctx->stream, op_ptr<const float>(a[0]), \
+              a[1], op_ptr<const float>(a[2]), a[3], op_ptr<const float>(a[4]), op_ptr<const float>(a[5]),              \
+              op_ptr<const float>(a[6]), op_ptr<float>(a[7]), a[8], op_ptr<const int>(a[9]), op_ptr<const int>(a[10]),   \
+              op_ptr<const int>(a[11]), op_ptr<float>(a[12]), a[13], H, P, N, G)
+    if (split == 1) SCOL_LAUNCH(1); else if (split == 2) SCOL_LAUNCH(2); else SCOL_LAUNCH(4);
+#undef SCOL_LAUNCH
+    GB_CHECK_LAUNCH("ssm_scan (columns)");
+    return 1;
+  }
   const dim3 grid(R, H, gb_div_up(P, SCAN_COLS)), block(32 * SCAN_WARPS);
   const size_t smem = sizeof(float) * (size_t)SCAN_TOKENS * (2 * N + SCAN_COLS + 2);      // at most 34 KB
 #define SCAN_LAUNCH(NPL)                                                                                              \
