@@ -183,8 +183,17 @@ def _ssm_params(m, d):
             "conv": m["conv"], "norm_groups": m.get("norm_groups", 1), "eps": 1e-5}
 
 
+def _ssm_cfg(state, vdim, heads=2, groups=1, conv=3):
+    return {"vocab": 16, "width": 48, "norm": {"eps": 1e-5}, "layers": [
+        {"type": "mamba2", "mixer": {"heads": heads, "vdim": vdim, "state": state, "groups": groups, "conv": conv,
+                                     "norm_groups": 1}, "mlp": None}]}
+
+
+# states of 20, 64 and 128 values run with the state in registers (one, two and four lanes a column); 70 (no multiple
+# of four) and 160 (more than 128) with the lanes over the state dimension; 128 x 72: more columns than a block takes
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("cfg,layer", [(CFG_A, 1), (CFG_B, 0)])
+@pytest.mark.parametrize("cfg,layer", [(CFG_A, 1), (CFG_B, 0), (_ssm_cfg(64, 8), 0), (_ssm_cfg(128, 72, heads=4, groups=2), 0),
+                                       (_ssm_cfg(160, 8), 0)])
 def test_state_space_mixer_alone_whole_cut_and_decoded(cfg, layer, dtype):
     m, d = cfg["layers"][layer]["mixer"], cfg["width"]
     W = _mixer_weights(cfg, layer, 8)
