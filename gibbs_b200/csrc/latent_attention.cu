@@ -177,6 +177,11 @@ __device__ __forceinline__ void load_row_vec(const float* src, float* dst, int D
 // (Measured against a variant that takes a tile's scores first, lane j keeping key j's, and then the
 // weighted sums in a second pass over the tile: 17.9 against 26.0 ms for four layers of a 2,048-token
 // prompt at 16 heads, latent 512 + 64, window 1,024.)
+// Exponentials of the softmax: the accurate one where the cache is 32-bit; where the cache rows are bfloat16
+// (2^-9 relative) the hardware's 2^x, whose error of a few 2^-23 relative is far below what the rows carry.
+template <typename TC> __device__ __forceinline__ float la_exp(float x) { return expf(x); }
+template <> __device__ __forceinline__ float la_exp<bf16>(float x) { return __expf(x); }
+
 constexpr int LA_HW = 2, LA_WARPS = 8, LA_HB = LA_HW * LA_WARPS, LA_KT = 32, LA_RR = 4;   // rotated part: up to 128
 
 template <typename TC, int RL>
@@ -276,13 +281,13 @@ latent_attention_kernel(const float* qp, const TC* pages, const int* block_table
         }
         const float sc = warp_sum(p0 + p1) * scale;       // every lane gets the same sum
         if (sc > m[hh]) {                                  // (the whole warp together)
-          const float corr = expf(m[hh] - sc);             // 0 for the first key: m = -inf
+          const float corr = la_exp<TC>(m[hh] - sc);       // 0 for the first key: m = -inf
           l[hh] *= corr;
 #pragma unroll
           for (int i = 0; i < RL; ++i) acc[hh][i] *= corr;
           m[hh] = sc;
         }
-        const float p = expf(sc - m[hh]);
+        const float p = la_exp<TC>(sc - m[hh]);
         l[hh] += p;
 #pragma unroll
         for (int i = 0; i < RL; ++i) acc[hh][i] = fmaf(p, kl[i], acc[hh][i]);
