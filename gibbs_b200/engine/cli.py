@@ -21,7 +21,7 @@ from pathlib import Path
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="gibbs-b200", description="gibbs-b200: LFM2 inference on one B200")
+    ap = argparse.ArgumentParser(prog="gibbs-b200", description="gibbs-b200: inference on one B200 (LFM2, Potivik)")
     ap.add_argument("-m", "--model", help="model folder (config.json + model.safetensors)")
     ap.add_argument("--prompt", help="prompt text (needs tokenizer.json in the model folder)")
     ap.add_argument("--prompt-ids", help="prompt as comma-separated token ids")

@@ -435,3 +435,33 @@ def test_greedy_generation_through_the_scheduler():
                 assert int(logits.argmax()) == tok, f"after {len(seq)} tokens"
             seq.append(tok)
         assert len(out) == 12
+
+
+def test_command_line_from_a_configuration_to_tokens(tmp_path, capsys):
+    """config.json -> random weights on disk -> --arch-dump, --probe-top5 and a greedy continuation, all
+    through the command line's own entry point."""
+    import json
+    from gibbs_b200.engine.cli import main
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(CFG_B))
+    folder = tmp_path / "model"
+    assert main(["--random", str(cfg_path), "--save", str(folder), "--seed", "3", "--dtype", "float32"]) == 0
+    capsys.readouterr()
+    assert main(["-m", str(folder), "--arch-dump"]) == 0
+    dump = json.loads(capsys.readouterr().out)
+    assert dump["architecture"] == "Potivik"
+    prompt = ids_for(CFG_B, 5, 9)
+    ids = ",".join(map(str, prompt))
+    assert main(["-m", str(folder), "--dtype", "float32", "--probe-top5", ids, "--ctx", "128"]) == 0
+    top = json.loads(capsys.readouterr().out)
+    from gibbs_b200.weights import Checkpoint
+    ck = Checkpoint(folder)
+    W = {n: ck.tensor(n) for n in ck.names()}
+    logits = plain.forward(CFG_B, W, prompt)[-1]
+    assert top["ids"][0] == int(logits.argmax())
+    assert abs(top["logits"][0] - float(logits.max())) < 1e-3
+    assert main(["-m", str(folder), "--dtype", "float32", "--prompt-ids", ids, "--max-tokens", "5", "--temperature", "0",
+                 "--ctx", "128"]) == 0
+    out = capsys.readouterr().out
+    generated = [int(t) for t in out.split("Output:\n")[1].splitlines()[0].split(",")]
+    assert len(generated) == 5 and generated[0] == top["ids"][0]
