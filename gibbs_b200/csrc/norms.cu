@@ -88,8 +88,17 @@ __global__ void row_norm_kernel(const float* x, long long ldx, const float* __re
   }
 }
 
+// `then`: the norm in front of the NEXT sublayer, taken of the new rows while they are in registers
+// (out2 = norm2(x) * gain2), so that it needs no kernel and no second trip of its own.
+struct ThenNorm {
+  const float* gain;
+  void* out;
+  int out_dtype, kind;
+  float eps;
+};
+
 __global__ void norm_add_kernel(float* x, long long ldx, const float* y, long long ldy, const float* __restrict__ gain,
-                                int dim, int kind, float eps, bf16* copy) {
+                                int dim, int kind, float eps, bf16* copy, ThenNorm then) {
   __shared__ float scratch[32];
   pdl_trigger();
   pdl_wait();
@@ -115,6 +124,22 @@ __global__ void norm_add_kernel(float* x, long long ldx, const float* y, long lo
         const float v = old[i] + (c.v[i] - mean) * rstd * gain[d];
         o[d] = v;
         if (copy) copy[(size_t)blockIdx.x * dim + d] = __float2bfloat16_rn(v);
+        c.v[i] = v;
+      } else {
+        c.v[i] = 0.f;
+      }
+    }
+    if (then.gain != nullptr) {                         // (only with the row in registers; the host sees to that)
+      float mean2, rstd2;
+      row_stats(o, c, dim, then.kind, then.eps, scratch, mean2, rstd2);
+#pragma unroll
+      for (int i = 0; i < NORM_CACHE; ++i) {
+        const int d = threadIdx.x + i * blockDim.x;
+        if (d < dim) {
+          const float h = (c.v[i] - mean2) * rstd2 * then.gain[d];
+          if (then.out_dtype == GB_BF16) ((bf16*)then.out)[(size_t)blockIdx.x * dim + d] = __float2bfloat16_rn(h);
+          else ((float*)then.out)[(size_t)blockIdx.x * dim + d] = h;
+        }
       }
     }
   } else {
@@ -199,15 +224,33 @@ GB_OP(gb_op_row_norm) {
 }
 
 // a0 x (f32, the stream), a1 its row stride, a2 y (f32), a3 its row stride, a4 gain, a5 rows, a6 dim, a7 kind,
-// a8 a bfloat16 copy of the new rows [rows, dim] for a product that reads the stream next, or 0; f0 eps
+// a8 a bfloat16 copy of the new rows [rows, dim] for a product that reads the stream next, or 0; a9 gain of a second
+// norm, taken of the new rows (the norm in front of the next sublayer), or 0; a10 its output [rows, dim], a11 the
+// output's dtype, a12 its kind; f0 eps, f1 the second norm's eps
 GB_OP(gb_op_norm_add) {
   const int n = (int)a[5], dim = (int)a[6], kind = (int)a[7];
   if (n <= 0) return 0;
   if (kind != NORM_LAYER && kind != NORM_RMS) GB_FAIL(GB_ERR_ARG, "norm_add: kind %d", kind);
-  gb_launch(norm_add_kernel, dim3(n), dim3(norm_threads(dim)), 0, ctx->stream, op_ptr<float>(a[0]), a[1],
-            op_ptr<const float>(a[2]), a[3], op_ptr<const float>(a[4]), dim, kind, (float)f[0], op_ptr<bf16>(a[8]));
+  const int threads = norm_threads(dim);
+  ThenNorm then = {op_ptr<const float>(a[9]), op_ptr<void>(a[10]), (int)a[11], (int)a[12], (float)f[1]};
+  const bool second = then.gain != nullptr;
+  if (second && then.kind != NORM_LAYER && then.kind != NORM_RMS) GB_FAIL(GB_ERR_ARG, "norm_add: second kind %d", then.kind);
+  const bool fused = second && dim <= NORM_CACHE * threads;   // the row fits the registers
+  ThenNorm none = {nullptr, nullptr, 0, 0, 0.f};
+  gb_launch(norm_add_kernel, dim3(n), dim3(threads), 0, ctx->stream, op_ptr<float>(a[0]), a[1],
+            op_ptr<const float>(a[2]), a[3], op_ptr<const float>(a[4]), dim, kind, (float)f[0], op_ptr<bf16>(a[8]),
+            fused ? then : none);
   GB_CHECK_LAUNCH("norm_add");
-  return 1;
+  if (!second || fused) return 1;
+  // a row too long for the registers: the second norm as a kernel of its own
+  if (then.out_dtype == GB_BF16)
+    gb_launch(row_norm_kernel<bf16>, dim3(n), dim3(threads), 0, ctx->stream, op_ptr<const float>(a[0]), a[1], then.gain,
+              (bf16*)then.out, (const int*)nullptr, dim, then.kind, then.eps);
+  else
+    gb_launch(row_norm_kernel<float>, dim3(n), dim3(threads), 0, ctx->stream, op_ptr<const float>(a[0]), a[1], then.gain,
+              (float*)then.out, (const int*)nullptr, dim, then.kind, then.eps);
+  GB_CHECK_LAUNCH("norm_add (second norm)");
+  return 2;
 }
 
 // a0 rows [g | u] (f32), a1 their stride, a2 out [n, inner], a3 out dtype, a4 its row stride, a5 rows, a6 inner;

@@ -4,6 +4,7 @@ from __future__ import annotations
 import torch
 
 from .base import Block, plan_ops_of, register_part
+from .norm import RowNorm
 from .runner import Eager, Planned, stream_tensor
 
 
@@ -75,9 +76,11 @@ class SandwichResidual(Block):
             copy = rn.buffer("stream_rows", hidden, torch.bfloat16)
         has_ffn = "ffn" in self.parts
         self.mixer.run(rn, h_of(self.mixer_norm), y, self.caches_of("mixer", caches))
-        self.mixer_post_norm.add_normed(rn, x, y, None if has_ffn else copy)
+        # the norm in front of the feed-forward is taken in the kernel that completes the stream behind the mixer
+        fuse = has_ffn and isinstance(self.ffn_norm, RowNorm) and self.ffn_norm.dim == hidden
+        h = self.mixer_post_norm.add_normed(rn, x, y, None if has_ffn else copy, self.ffn_norm if fuse else None)
         if has_ffn:
-            self.ffn.run(rn, h_of(self.ffn_norm), y, None)
+            self.ffn.run(rn, h if fuse else h_of(self.ffn_norm), y, None)
             self.ffn_post_norm.add_normed(rn, x, y, copy)
         if "token_input" in self.parts:
             self.token_input.run(rn, x, copy)

@@ -78,12 +78,21 @@ class RowNorm(Norm):
               [self.eps], label="row_norm")
         return out
 
-    def add_normed(self, rn: Runner, x: torch.Tensor, y: torch.Tensor, copy: torch.Tensor = None) -> None:
+    def add_normed(self, rn: Runner, x: torch.Tensor, y: torch.Tensor, copy: torch.Tensor = None, then=None):
         """x += norm(y) * gain, for x the stream and y a sublayer's output (both float32).  ``copy``
         (bfloat16 [rows, dim], contiguous) also receives the new rows, for a product that reads
-        the stream next."""
-        rn.op("norm_add", [x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), keep(rn, self.gain), rn.N, self.dim,
-                           self.KIND, 0 if copy is None else copy.data_ptr()], [self.eps], label="norm_add")
+        the stream next.  ``then`` (another RowNorm: the norm in front of the next sublayer) is taken
+        of the new rows in the same kernel; its output is returned."""
+        a = [x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), keep(rn, self.gain), rn.N, self.dim, self.KIND,
+             0 if copy is None else copy.data_ptr()]
+        f = [self.eps]
+        out = None
+        if then is not None:
+            out = rn.buffer("normed", then.dim)
+            a += [keep(rn, then.gain), out.data_ptr(), ops.dtype_code(out.dtype), then.KIND]
+            f += [then.eps]
+        rn.op("norm_add", a, f, label="norm_add")
+        return out
 
     def forward(self, x, out=None, rows=None):
         x = stream_tensor(x)
