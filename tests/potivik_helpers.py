@@ -77,6 +77,41 @@ CFG_C = {
 CONFIGS = {"A": (CFG_A, 11), "B": (CFG_B, 12), "C": (CFG_C, 13)}
 
 
+def random_config(seed: int) -> dict:
+    """A configuration of the design with every size, option and the order of layers drawn at random."""
+    import random
+    rng = random.Random(seed)
+    d = rng.choice([24, 32, 40, 64, 72, 128])
+    layers = []
+    for _ in range(rng.randint(1, 5)):
+        if rng.random() < 0.5:
+            dr = rng.choice([2, 4, 6, 8, 16]); dims = rng.choice([x for x in range(2, dr + 1, 2)])
+            m = {"heads": rng.choice([1, 2, 3, 5, 8, 17]), "dim": rng.choice([2, 4, 7, 8, 16, 24]), "rot_dim": dr,
+                 "vdim": rng.choice([1, 3, 8, 16]), "kv_rank": rng.choice([4, 8, 12, 33, 64, 96]), "scale": rng.choice([0.2, 0.35, 0.5]),
+                 "rot": {"base": rng.choice([10.0, 1000.0, 500000.0]), "dims": dims}}
+            w = rng.choice([None, 1, 2, 7, 16, 17, 40, 100])
+            if w: m["mask"] = {"size": w}
+            layers.append({"type": "latent_attention", "mixer": m})
+        else:
+            heads = rng.choice([1, 2, 4, 6]); groups = rng.choice([g for g in (1, 2, 3, 6) if heads % g == 0])
+            P = rng.choice([1, 3, 4, 8, 12, 20]); inner = heads * P
+            ng = rng.choice([g for g in (1, 2, 3, 4) if inner % g == 0])
+            layers.append({"type": "mamba2", "mixer": {"heads": heads, "vdim": P, "state": rng.choice([1, 4, 8, 16, 24, 33, 64, 128, 132]),
+                                                        "groups": groups, "conv": rng.randint(1, 5), "norm_groups": ng}})
+        k = rng.random()
+        if k < 0.2: layers[-1]["mlp"] = None
+        elif k < 0.5: layers[-1]["mlp"] = {"kind": "dense", "ff": rng.choice([8, 20, 64, 128]), "limit": rng.choice([0.5, 1.0, 4.0])}
+        else:
+            E = rng.choice([1, 2, 3, 8, 16, 33]); top = rng.randint(1, min(E, 4))
+            f = {"kind": "moe", "router": {"experts": E, "top": top}, "expert": {"ff": rng.choice([4, 9, 16, 64]), "limit": rng.choice([1.0, 3.0])}}
+            if rng.random() < 0.5: f["shared"] = {"ff": rng.choice([8, 24, 64]), "limit": rng.choice([1.0, 3.0])}
+            layers[-1]["mlp"] = f
+    cfg = {"architecture": "Potivik", "vocab": rng.choice([50, 97, 256]), "width": d, "norm": {"eps": rng.choice([1e-5, 1e-6])}, "layers": layers}
+    if rng.random() < 0.6: cfg["token_side"] = {"dim": rng.choice([1, 3, 8, 16])}
+    if rng.random() < 0.6: cfg["logit_softcap"] = rng.choice([5.0, 30.0])
+    return cfg
+
+
 def _bf16_exact(t: torch.Tensor) -> torch.Tensor:
     return t.to(torch.bfloat16).to(torch.float32)
 

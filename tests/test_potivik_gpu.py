@@ -402,6 +402,35 @@ def test_mixed_batches_with_pages_and_slots_used_again(name, dtype):
             assert (e > lim).mean() <= (0.0 if dtype == "float32" else 0.45), f"{rid}: batch against alone {e.max():.3g}"
 
 
+@pytest.mark.parametrize("seed", [3, 9, 11, 14, 37, 74])
+def test_random_configurations_in_float32(seed):
+    """Sizes, options and the order of layers drawn at random (one to five layers; one to seventeen heads;
+    windows of one token and none; one expert, all experts chosen; states of 1 to 132 values; ...), whole,
+    cut, decoded and in mixed batches.  Held to the plain implementation in float64, or to ten times what
+    the plain implementation itself loses in float32 where a configuration is ill-conditioned (a norm
+    over a handful of values)."""
+    from potivik_helpers import random_config
+    from gibbs_b200.config import parse_config
+    from gibbs_b200.parts.model import build_model
+    from gibbs_b200.weights import TensorDict
+    cfg = random_config(seed)
+    W = make_weights(cfg, seed)
+    model = build_model(parse_config(cfg).plan(), TensorDict({k: v.to(torch.bfloat16) for k, v in W.items()}),
+                        torch.float32, DEV)
+    reqs = {f"r{n}": ids_for(cfg, seed * 7 + n, n) for n in (1, 2, 37, 90)}
+    truth = {rid: plain.forward(cfg, W, ids).numpy() for rid, ids in reqs.items()}
+    own = {rid: rel_rows(plain.forward(cfg, W, ids, dtype=torch.float32).numpy(), truth[rid]).max()
+           for rid, ids in reqs.items()}
+    for what, steps in (("whole", trace_whole(reqs)), ("cut", trace_portions(reqs)),
+                        ("decoded", trace_tail_decoded(reqs, tail=30)),
+                        ("mixed", trace_mixed(reqs, capacity_tokens=256, max_live=3, seed=seed))):
+        eng = engine_for(model, n_pages=16, max_requests=3, cap=256)
+        got = run_trace_on_engine(eng, steps)
+        for rid in reqs:
+            e = rel_rows(got[rid], truth[rid]).max()
+            assert e <= max(3e-4, 10 * own[rid]), f"{what} {rid}: {e:.3g} (the plain implementation in float32: {own[rid]:.3g})"
+
+
 def test_long_decoding_past_windows_pages_and_chunks():
     """260 tokens decoded one by one after a two-token prompt: every window edge, page edge and slot
     state is passed by single tokens."""
