@@ -3,12 +3,17 @@
 //  gb_op_moe_route     per token: the `top` largest router logits (ties: the lower index), their
 //                      sigmoids as weights (not renormalised), and the sigmoid of the shared expert's
 //                      gate logit; all in 32-bit
+//  gb_op_moe_route_grouped  the same choice for routers with softmax (or sigmoid) scores, a correction added to
+//                      the scores for the choice only, experts in groups of which only the best are open, and
+//                      trailing "identity" outputs that stand for experts returning their input
 //  gb_op_moe_sort      (token, choice) pairs ordered by expert: offsets[E + 1], the pair behind every
 //                      row, the row of every pair
 //  gb_op_moe_gather    rows[row] = weight * h[token]: the weight multiplies the expert's INPUT
 //  gb_op_moe_experts   per expert, over its rows: either act = glu(rows W_gate^T, rows W_up^T) with
 //                      clamps, or out = rows W_down^T (32-bit)
 //  gb_op_moe_combine   y[token] = sum over its choices of out[row] (+ gate * shared[token])
+//  gb_op_moe_combine_weighted  y[token] (+)= sum over its choices of weight * out[row], where the weight multiplies
+//                      the expert's OUTPUT; a choice beyond the real experts contributes weight * h[token]
 //
 // A row's result does not depend on which rows share its tile (one accumulator per output walking k
 // upwards), so the order in which pairs land inside an expert's range does not matter.
@@ -51,6 +56,93 @@ __global__ void moe_route_kernel(const float* logits, long long ld, int n, int E
   if (shared_gate && lane == 0) shared_gate[t] = hy_sigmoid(z[shared_col]);
 }
 
+// One warp per token.  scores: 0 sigmoid(z), 1 softmax(z) over all `n_out` router outputs.  The choice is made on
+// score + correction; with `groups` > 1 the outputs form that many equal groups of neighbours, a group's mark is
+// its largest choice score, and only outputs of the `keep` best groups can be chosen.  The weight of a chosen
+// output is its score without the correction, not renormalised.  Ties go to the lower index.
+__global__ void moe_route_grouped_kernel(const float* logits, long long ld, int n, int n_out, int top, int scores,
+                                         const float* __restrict__ correction, int groups, int keep, int* idx,
+                                         float* weight) {
+  extern __shared__ float route_sm[];                    // per warp: scores [n_out], choice scores [n_out], group marks
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= n) return;
+  float* s = route_sm + (size_t)warp * (2 * n_out + groups);
+  float* c = s + n_out;
+  float* mark = c + n_out;
+  const float* z = logits + (size_t)t * ld;
+  if (scores == 1) {
+    float mx = -INFINITY;
+    for (int e = lane; e < n_out; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < n_out; e += 32) {
+      const float v = expf(z[e] - mx);
+      s[e] = v;
+      sum += v;
+    }
+    sum = warp_sum(sum);
+    for (int e = lane; e < n_out; e += 32) s[e] = s[e] / sum;
+  } else {
+    for (int e = lane; e < n_out; e += 32) s[e] = hy_sigmoid(z[e]);
+  }
+  for (int e = lane; e < n_out; e += 32) c[e] = s[e] + (correction ? correction[e] : 0.f);
+  __syncwarp();
+  const int gs = n_out / groups;
+  if (groups > 1 && keep < groups) {
+    for (int g = lane; g < groups; g += 32) {
+      float b = -INFINITY;
+      for (int e = g * gs; e < (g + 1) * gs; ++e) b = fmaxf(b, c[e]);
+      mark[g] = b;
+    }
+    __syncwarp();
+    // the groups that stay closed: all but the `keep` best (a closed group's mark becomes NaN-free -inf, an
+    // open one's +inf, so that the pass below reads one flag per group)
+    for (int k = 0; k < keep; ++k) {
+      float bv = -INFINITY;
+      int bg = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32) {
+        const float v = mark[g];
+        if (v != INFINITY && (bg == 0x7fffffff || v > bv)) { bv = v; bg = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int og = __shfl_xor_sync(0xffffffffu, bg, o);
+        if (og != 0x7fffffff && (bg == 0x7fffffff || ov > bv || (ov == bv && og < bg))) { bv = ov; bg = og; }
+      }
+      if (lane == 0 && bg != 0x7fffffff) mark[bg] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < n_out; e += 32)
+      if (mark[e / gs] != INFINITY) c[e] = -INFINITY;     // (a closed output; an open one keeps its own score)
+    __syncwarp();
+  }
+  for (int k = 0; k < top; ++k) {
+    float bv = -INFINITY;
+    int be = 0x7fffffff;
+    for (int e = lane; e < n_out; e += 32) {
+      const float v = c[e];
+      if (v != -INFINITY || be == 0x7fffffff)
+        if (be == 0x7fffffff || v > bv) { bv = v; be = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (oe != 0x7fffffff && (be == 0x7fffffff || ov > bv || (ov == bv && oe < be))) { bv = ov; be = oe; }
+    }
+    if (lane == 0) {
+      idx[(size_t)t * top + k] = be;
+      weight[(size_t)t * top + k] = s[be];
+      c[be] = -INFINITY;                                   // taken
+    }
+    __syncwarp();
+  }
+}
+
 // one block
 __global__ void moe_sort_kernel(const int* idx, int pairs, int E, int* offsets, int* row_pair, int* pair_row) {
   __shared__ int count[MOE_MAX_EXPERTS + 1];
@@ -85,7 +177,7 @@ __global__ void moe_gather_kernel(const T* h, long long ldh, const int* row_pair
   pdl_wait();
   const int row = blockIdx.x;
   const int p = row_pair[row];
-  const float w = weight[p];
+  const float w = weight ? weight[p] : 1.f;              // (no weights: they multiply the experts' outputs instead)
   const T* src = h + (size_t)(p / top) * ldh;
   T* dst = rows + (size_t)row * ldr;
   for (int d = threadIdx.x; d < width; d += blockDim.x) dst[d] = from_f32<T>(w * to_f32(src[d]));
@@ -181,7 +273,48 @@ __global__ void moe_combine_kernel(const float* out, long long ldo, const int* p
   }
 }
 
+template <typename T>
+__global__ void moe_combine_weighted_kernel(const float* out, long long ldo, const int* pair_row, const int* idx,
+                                            const float* weight, const T* h, long long ldh, float* y, long long ldy,
+                                            int width, int top, int E, int accumulate) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) {
+    float v = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const size_t p = (size_t)t * top + k;
+      const float src = idx[p] < E ? out[(size_t)pair_row[p] * ldo + d] : to_f32(h[(size_t)t * ldh + d]);
+      v = fmaf(weight[p], src, v);
+    }
+    float* o = y + (size_t)t * ldy + d;
+    *o = accumulate ? *o + v : v;
+  }
+}
+
 }  // namespace
+
+// a0 logits (f32), a1 their row stride, a2 tokens, a3 router outputs (experts and identity outputs), a4 top, a5 scores
+// (0 sigmoid, 1 softmax), a6 correction [outputs] (f32) or 0, a7 groups (1: none), a8 groups kept, a9 chosen outputs
+// [tokens, top] (int32), a10 their weights (f32)
+GB_OP(gb_op_moe_route_grouped) {
+  const int n = (int)a[2], n_out = (int)a[3], top = (int)a[4];
+  int groups = (int)a[7], keep = (int)a[8];
+  if (n <= 0) return 0;
+  if (groups < 1) groups = 1;
+  if (keep < 1 || keep > groups) keep = groups;
+  if (n_out > MOE_MAX_EXPERTS) GB_FAIL(GB_ERR_ARG, "moe_route_grouped: %d router outputs (at most %d)", n_out, MOE_MAX_EXPERTS);
+  if (n_out % groups) GB_FAIL(GB_ERR_ARG, "moe_route_grouped: %d router outputs in %d groups", n_out, groups);
+  if (top < 1 || top > (n_out / groups) * keep)
+    GB_FAIL(GB_ERR_ARG, "moe_route_grouped: top %d of the %d outputs in %d open groups", top, (n_out / groups) * keep, keep);
+  const int warps = 4;
+  const size_t smem = sizeof(float) * warps * (2 * (size_t)n_out + groups);
+  gb_launch(moe_route_grouped_kernel, dim3(gb_div_up(n, warps)), dim3(32 * warps), smem, ctx->stream,
+            op_ptr<const float>(a[0]), a[1], n, n_out, top, (int)a[5], op_ptr<const float>(a[6]), groups, keep,
+            op_ptr<int>(a[9]), op_ptr<float>(a[10]));
+  GB_CHECK_LAUNCH("moe_route_grouped");
+  return 1;
+}
 
 // a0 logits (f32), a1 their row stride, a2 tokens, a3 experts, a4 top, a5 column of the shared expert's gate logit,
 // a6 chosen experts [tokens, top] (int32), a7 their weights (f32), a8 shared gate [tokens] (f32), or 0 for none
@@ -207,7 +340,7 @@ GB_OP(gb_op_moe_sort) {
   return 1;
 }
 
-// a0 h, a1 its row stride, a2 dtype (of h and rows), a3 row -> pair, a4 weights [pairs], a5 rows out, a6 their
+// a0 h, a1 its row stride, a2 dtype (of h and rows), a3 row -> pair, a4 weights [pairs] or 0 (plain copies), a5 rows out, a6 their
 // stride, a7 tokens, a8 width, a9 top
 GB_OP(gb_op_moe_gather) {
   const int pairs = (int)(a[7] * a[9]), width = (int)a[8];
@@ -261,5 +394,24 @@ GB_OP(gb_op_moe_combine) {
             op_ptr<const int>(a[2]), op_ptr<const float>(a[3]), op_ptr<const float>(a[4]), a[5], op_ptr<float>(a[6]), a[7],
             width, (int)a[10]);
   GB_CHECK_LAUNCH("moe_combine");
+  return 1;
+}
+
+// a0 expert outputs by row (f32), a1 their stride, a2 pair -> row, a3 chosen outputs [tokens, top], a4 their weights,
+// a5 the feed-forward's input h, a6 its row stride, a7 its dtype, a8 y (f32), a9 its row stride, a10 tokens, a11 width,
+// a12 top, a13 real experts (a choice from here on returns h); flags bit 0: add into y
+GB_OP(gb_op_moe_combine_weighted) {
+  const int n = (int)a[10], width = (int)a[11];
+  if (n <= 0) return 0;
+  const dim3 grid(n), block(width <= 256 ? 64 : 256);
+  if (a[7] == GB_BF16)
+    gb_launch(moe_combine_weighted_kernel<bf16>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1],
+              op_ptr<const int>(a[2]), op_ptr<const int>(a[3]), op_ptr<const float>(a[4]), op_ptr<const bf16>(a[5]), a[6],
+              op_ptr<float>(a[8]), a[9], width, (int)a[12], (int)a[13], flags & 1);
+  else
+    gb_launch(moe_combine_weighted_kernel<float>, grid, block, 0, ctx->stream, op_ptr<const float>(a[0]), a[1],
+              op_ptr<const int>(a[2]), op_ptr<const int>(a[3]), op_ptr<const float>(a[4]), op_ptr<const float>(a[5]), a[6],
+              op_ptr<float>(a[8]), a[9], width, (int)a[12], (int)a[13], flags & 1);
+  GB_CHECK_LAUNCH("moe_combine_weighted");
   return 1;
 }

@@ -12,6 +12,7 @@ class PreNormResidual(Block):
     """x += mixer(norm(x)); x += ffn(norm(x))
     (MisterTK/gibbs arch/families/lfm2.json5:76-89)."""
     ROLES = (("mixer_norm", "norm"), ("mixer", "mixer"), ("ffn_norm", "norm"), ("ffn", "feed_forward"))
+    OPTIONAL_ROLES = ("ffn_norm", "ffn")       # a layer may have no feed-forward (then neither its norm)
 
     # A mixer or feed-forward that says ``fuses_norm`` hands its input straight to a product
     # (``parts.linear.Linear``), which may then run the norm itself.
@@ -19,12 +20,16 @@ class PreNormResidual(Block):
     def forward(self, x, step, caches):
         h = self.mixer_norm.lazy(x) if getattr(self.mixer, "fuses_norm", False) else self.mixer_norm.forward(x)
         self.mixer.forward(h, x, step, self.caches_of("mixer", caches))
+        if "ffn" not in self.parts:
+            return
         h = self.ffn_norm.lazy(x) if getattr(self.ffn, "fuses_norm", False) else self.ffn_norm.forward(x)
         self.ffn.forward(h, x, step)
 
     def plan_ops(self, plan, caches):
         h = self._norm_ops(plan, self.mixer_norm, self.mixer)
         plan_ops_of(self.mixer)(plan, h, self.caches_of("mixer", caches))
+        if "ffn" not in self.parts:
+            return
         h = self._norm_ops(plan, self.ffn_norm, self.ffn)
         plan_ops_of(self.ffn)(plan, h)
 

@@ -4,12 +4,15 @@ from __future__ import annotations
 import torch
 
 from .. import ops
+from ..ops import hybrid
+from .runner import Planned, keep
 from .base import Part, TensorDecl, register_part
 from .linear import Linear
 
 
 class TokenEmbedding(Part):
-    """x[t, :] = table[id_t, :], no scaling (MisterTK/gibbs arch/families/lfm2.json5:74)."""
+    """x[t, :] = table[id_t, :] (MisterTK/gibbs arch/families/lfm2.json5:74), times ``scale`` for a
+    design that has one (default 1: no scaling)."""
     category = "embedding"
 
     @classmethod
@@ -20,13 +23,30 @@ class TokenEmbedding(Part):
         super().__init__(params, tensors, rt)
         self.vocab, self.dim = int(params["vocab"]), int(params["dim"])
         self.table = tensors["weight"].contiguous()
+        self.scale = float(params.get("scale", 1.0) or 1.0)
+
+    def kernel_libraries(self):
+        return ("core",) if self.scale == 1.0 else ("core", hybrid.LIBRARY)
+
+    def _scaled(self, rn, ids: int, out: torch.Tensor) -> None:
+        rn.op("embed_scaled", [keep(rn, self.table), ops.dtype_code(self.table.dtype), ids, out.data_ptr(), rn.N,
+                               self.dim, self.vocab], [self.scale])
 
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
         out = self.rt.empty(ids.numel(), self.dim, dtype=torch.float32)
-        return ops.embed(self.table, ids, out)
+        if self.scale == 1.0:
+            return ops.embed(self.table, ids, out)
+        hybrid.call("embed_scaled", [self.table.data_ptr(), ops.dtype_code(self.table.dtype), ids.data_ptr(),
+                                     out.data_ptr(), ids.numel(), self.dim, self.vocab], [self.scale],
+                    device=self.rt.device)
+        return out
 
     def plan_ops(self, plan):
-        plan.embed(self.table)
+        if self.scale == 1.0:
+            plan.embed(self.table)
+        else:
+            rn = Planned(plan)
+            self._scaled(rn, rn.token_ids, plan.residual)
 
 
 class LMHead(Part):

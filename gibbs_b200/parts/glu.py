@@ -13,10 +13,24 @@ expert_e(s_e * h).  An optional shared expert runs for every token and is added
 times sigmoid(W_sg h), one number per token.  Tokens are ordered by expert on
 the device (no host round trip), the experts' products run over the ragged row
 ranges (csrc/moe.cu).
+
+The router's rule is made of parameters, so that other designs can set it:
+``scores`` "sigmoid" (default) or "softmax" (over all router outputs);
+``correction``: a vector added to the scores for the CHOICE only (the weights
+use the scores without it); ``groups`` / ``groups_keep``: the router outputs
+form that many equal groups of neighbours, a group's mark is its largest choice
+score, and only outputs of the best ``groups_keep`` groups can be chosen;
+``identity``: that many router outputs behind the experts' stand for experts
+that return their input (they have no tensors; they count in the softmax and in
+the groups); ``weight_on`` "input" (default: s_e multiplies the expert's input)
+or "output" (out = sum_e s_e * expert_e(h)); ``limit`` 0 or absent: no clamp.
+A routed unit whose weights are on the output can add its result straight
+into the residual stream (``adds_in_place``).
 """
 from __future__ import annotations
 
 import ctypes
+import math
 
 import torch
 
@@ -66,7 +80,9 @@ class RoutedGLU(BranchPart, FeedForward):
     @classmethod
     def declare(cls, params):
         h, E, f = params["hidden"], params["experts"], params["expert_inner"]
-        d = {"router": TensorDecl.of(E, h)}
+        d = {"router": TensorDecl.of(E + int(params.get("identity", 0) or 0), h)}
+        if params.get("correction"):
+            d["correction"] = TensorDecl.of(E + int(params.get("identity", 0) or 0), role=VECTOR)
         for e in range(E):
             d.update({f"e{e}.gate": TensorDecl.of(f, h), f"e{e}.up": TensorDecl.of(f, h), f"e{e}.down": TensorDecl.of(h, f)})
         if params.get("shared_inner"):
@@ -79,10 +95,24 @@ class RoutedGLU(BranchPart, FeedForward):
         super().__init__(params, tensors, rt)
         p = params
         self.hidden, self.E, self.top, self.inner = int(p["hidden"]), int(p["experts"]), int(p["top"]), int(p["expert_inner"])
-        self.limit = float(p["expert_limit"])
+        self.limit = float(p.get("expert_limit") or 0.0) or math.inf
         self.alpha, self.up_add = float(p.get("alpha", 1.702)), float(p.get("up_add", 1.0))
-        if not 1 <= self.top <= self.E:
-            raise ValueError(f"top {self.top} of {self.E} experts")
+        self.identity = int(p.get("identity", 0) or 0)
+        self.n_out = self.E + self.identity                      # router outputs
+        self.scores = {"sigmoid": 0, "softmax": 1}[p.get("scores", "sigmoid")]
+        self.groups = int(p.get("groups", 1) or 1)
+        self.groups_keep = int(p.get("groups_keep", self.groups) or self.groups)
+        self.weight_on_output = {"input": False, "output": True}[p.get("weight_on", "input")]
+        self.correction = tensors["correction"].to(torch.float32).contiguous() if p.get("correction") else None
+        if self.n_out % self.groups or not 1 <= self.groups_keep <= self.groups:
+            raise ValueError(f"{self.n_out} router outputs in {self.groups} groups of which {self.groups_keep} stay open")
+        if not 1 <= self.top <= (self.n_out // self.groups) * self.groups_keep:
+            raise ValueError(f"top {self.top} of {self.n_out} router outputs ({self.groups_keep} of {self.groups} groups open)")
+        if self.identity and not self.weight_on_output:
+            raise ValueError("identity experts come with weights on the experts' outputs")
+        # the plain rule (sigmoid scores, the largest win) has a kernel of its own
+        self.plain_rule = (self.scores == 0 and self.correction is None and self.groups == 1 and not self.identity)
+        self.adds_in_place = self.weight_on_output
         E = self.E
         # gate and up rows of an expert side by side; in blocks of 64 features where the width allows, the
         # layout the tensor-core kernel's epilogue wants (csrc/moe_tc.cu)
@@ -115,23 +145,33 @@ class RoutedGLU(BranchPart, FeedForward):
             total += tensor_bytes(self.shared, seen)
         return total
 
-    def run(self, rn: Runner, h, out, caches=None):
-        E, top, d, f = self.E, self.top, self.hidden, self.inner
+    def run(self, rn: Runner, h, out, caches=None, accumulate: bool = False):
+        E, top, d, f, n_out = self.E, self.top, self.hidden, self.inner, self.n_out
         shared = self.shared is not None
-        logits = rn.buffer("moe_logits", E + (1 if shared else 0), torch.float32)
+        if accumulate and not self.weight_on_output:
+            raise ValueError("a routed unit with weights on the experts' inputs writes its output")
+        logits = rn.buffer("moe_logits", n_out + (1 if shared else 0), torch.float32)
         rn.linear(h, self.w_router, None, logits, role="router")
         idx = rn.buffer("moe_choice", top, torch.int32)
         wts = rn.buffer("moe_weight", top, torch.float32)
         sg = rn.buffer("moe_shared_gate", 1, torch.float32)
-        rn.op("moe_route", [logits.data_ptr(), logits.stride(0), rn.N, E, top, E, idx.data_ptr(), wts.data_ptr(),
-                            sg.data_ptr() if shared else 0])
-        offsets = rn.buffer("moe_offsets", E + 1, torch.int32, fixed_rows=1)
+        if self.plain_rule:
+            rn.op("moe_route", [logits.data_ptr(), logits.stride(0), rn.N, E, top, E, idx.data_ptr(), wts.data_ptr(),
+                                sg.data_ptr() if shared else 0])
+        else:
+            if shared:
+                raise ValueError("a shared expert's gate comes with the plain router rule")
+            rn.op("moe_route_grouped", [logits.data_ptr(), logits.stride(0), rn.N, n_out, top, self.scores,
+                                        keep(rn, self.correction), self.groups, self.groups_keep, idx.data_ptr(),
+                                        wts.data_ptr()])
+        # (identity outputs are sorted behind the experts: their rows lie beyond offsets[E] and no product reads them)
+        offsets = rn.buffer("moe_offsets", n_out + 1, torch.int32, fixed_rows=1)
         row_pair = rn.buffer("moe_row_pair", top, torch.int32)
         pair_row = rn.buffer("moe_pair_row", top, torch.int32)
-        rn.op("moe_sort", [idx.data_ptr(), rn.N, E, offsets.data_ptr(), row_pair.data_ptr(), pair_row.data_ptr(), top])
+        rn.op("moe_sort", [idx.data_ptr(), rn.N, n_out, offsets.data_ptr(), row_pair.data_ptr(), pair_row.data_ptr(), top])
         rows = rn.buffer("moe_rows", d, per_token=top)
-        rn.op("moe_gather", [h.data_ptr(), h.stride(0), ops.dtype_code(h.dtype), row_pair.data_ptr(), wts.data_ptr(),
-                             rows.data_ptr(), rows.stride(0), rn.N, d, top])
+        rn.op("moe_gather", [h.data_ptr(), h.stride(0), ops.dtype_code(h.dtype), row_pair.data_ptr(),
+                             0 if self.weight_on_output else wts.data_ptr(), rows.data_ptr(), rows.stride(0), rn.N, d, top])
         act = rn.buffer("moe_act", f, per_token=top)
         wdt = ops.dtype_code(self.w_down.dtype)
         eout = rn.buffer("moe_expert_out", d, torch.float32, per_token=top)
@@ -155,6 +195,13 @@ class RoutedGLU(BranchPart, FeedForward):
             rn.op("moe_experts", [act.data_ptr(), act.stride(0), ops.dtype_code(act.dtype), keep(rn, self.w_down), wdt,
                                   offsets.data_ptr(), E, eout.data_ptr(), eout.stride(0), rn.N, d, f, 1, top, 0],
                   label="moe_experts:down")
+        if self.weight_on_output:
+            if shared:
+                raise ValueError("a shared expert comes with weights on the experts' inputs")
+            rn.op("moe_combine_weighted", [eout.data_ptr(), eout.stride(0), pair_row.data_ptr(), idx.data_ptr(),
+                                           wts.data_ptr(), h.data_ptr(), h.stride(0), ops.dtype_code(h.dtype),
+                                           out.data_ptr(), out.stride(0), rn.N, d, top, E], flags=1 if accumulate else 0)
+            return
         sh = None
         if shared:
             sh = rn.buffer("moe_shared_out", d, torch.float32)

@@ -39,7 +39,7 @@ class Runner:
         blocks of 64 (``parts.linear.interleave_gate_up``); ``glu`` = (alpha, limit, add)."""
         raise NotImplementedError
 
-    def op(self, name: str, a, f=(), label: str = "") -> None:
+    def op(self, name: str, a, f=(), label: str = "", flags: int = 0) -> None:
         raise NotImplementedError
 
     def table(self, view):
@@ -69,8 +69,8 @@ class Eager(Runner):
     def glu_linear(self, x, weight, out, glu, role=""):
         ops.linear_tc(x[:self.N] if x.shape[0] != self.N else x, weight, None, out, swiglu=True, glu=glu)
 
-    def op(self, name, a, f=(), label=""):
-        hybrid.call(name, a, f, device=self.rt.device)
+    def op(self, name, a, f=(), label="", flags=0):
+        hybrid.call(name, a, f, flags=flags, device=self.rt.device)
 
     def table(self, view):
         bt = view.block_table
@@ -101,8 +101,8 @@ class Planned(Runner):
     def glu_linear(self, x, weight, out, glu, role=""):
         self.plan.linear(x, weight, None, out, "swiglu", role=role or "glu", glu=glu)
 
-    def op(self, name, a, f=(), label=""):
-        self.plan.emit(hybrid.plan_id(name), list(a), list(f), label=label or name)
+    def op(self, name, a, f=(), label="", flags=0):
+        self.plan.emit(hybrid.plan_id(name), list(a), list(f), flags=flags, label=label or name)
 
     def table(self, view):
         if not isinstance(view.block_table, self._P.TableRef):
@@ -135,10 +135,16 @@ class BranchPart:
     arrangement can put a norm between the sublayer and the residual sum.  In an arrangement
     that adds sublayers straight into the stream, ``forward`` adds ``out`` to it."""
     writes_branch = True
+    # True for a part whose ``run`` takes ``accumulate=True`` and then ADDS its output into ``out``: in an
+    # arrangement that sums sublayers straight into the stream its last kernel does the residual sum
+    adds_in_place = False
 
     def forward(self, h, residual, step, caches=None):
         rn = Eager(self.rt, step)
         if isinstance(residual, Residual):
+            if self.adds_in_place:
+                self.run(rn, h, residual.tensor(), caches, accumulate=True)
+                return
             y = rn.buffer("branch", residual.shape[1], torch.float32)
             self.run(rn, h, y, caches)
             ops.add_pending(residual.tensor(), y.unsqueeze(0), None)
@@ -147,6 +153,10 @@ class BranchPart:
 
     def plan_ops(self, plan, h, caches=None, out=None):
         if out is None:
-            raise NotPlannable(f"{type(self).__name__} writes its output for a norm to add; a plan needs an "
-                               "arrangement that takes it")
+            if not self.adds_in_place:
+                raise NotPlannable(f"{type(self).__name__} writes its output for a norm to add; a plan needs an "
+                                   "arrangement that takes it")
+            # (an operation of the hybrid library finds the stream whole: the walker adds what a product left)
+            self.run(Planned(plan), h, plan.residual, caches, accumulate=True)
+            return
         self.run(Planned(plan), h, out, caches)
