@@ -100,11 +100,17 @@ __global__ void qk_prep_kernel(const float* fused, long long ld, int k_col, int 
 // one query head.  Keys and values arrive in tiles of 32 positions in shared memory (32-bit), shared by the
 // block's heads.  Lane j takes key j's score (the query is read from shared memory, the same address for
 // all lanes; key rows lie an odd number of words apart); the tile's weights then enter the weighted sum of
-// values with the lanes over the value's entries.  The running maximum starts at the sink's score when
-// there is one, so that no exponential exceeds 1.
+// values with the lanes over the value's entries.  The sink joins at the end, by the same arithmetic as in
+// the merge of chunks (sa_finish), so that a launch with one chunk and a launch with several whose other
+// chunks are empty give the same bits.
 constexpr int SA_WARPS = 8, SA_KT = 32;
 
 template <typename TC> __device__ __forceinline__ float sa_exp(float x) { return expf(x); }
+
+// The sums over chunks s of exp(m_s - M) * (l_s, acc_s) with M = max(m_s, the sink's 0): what both the
+// attention kernel (one chunk) and the merge kernel (several) divide by and multiply with.
+__device__ __forceinline__ float sa_top(float m, int sink) { return sink ? fmaxf(m, 0.f) : m; }
+__device__ __forceinline__ float sa_sink_weight(float M, int sink) { return sink ? expf(0.f - M) : 0.f; }
 
 template <typename TC, typename TQ, typename TO, int VR>
 __global__ void __launch_bounds__(32 * SA_WARPS)
@@ -141,8 +147,7 @@ sink_attention_kernel(const TQ* q, long long ldq, const TC* k_pages, const TC* v
   float acc[VR];
 #pragma unroll
   for (int i = 0; i < VR; ++i) acc[i] = 0.f;
-  const bool own_sink = sink && splits == 1;                  // (with chunks the merge adds the sink)
-  float m = own_sink ? 0.f : -INFINITY, l = own_sink ? 1.f : 0.f;
+  float m = -INFINITY, l = 0.f;
   for (int k0 = k_begin; k0 <= k_end; k0 += SA_KT) {
     __syncthreads();                                          // the last tile has been used (and qs is written)
     if (threadIdx.x < SA_KT) {
@@ -207,13 +212,15 @@ sink_attention_kernel(const TQ* q, long long ldq, const TC* k_pages, const TC* v
     }
     return;
   }
-  const float inv = 1.0f / l;
+  const float M = sa_top(m, sink);
+  const float e = expf(m - M);
+  const float inv = 1.0f / fmaf(e, l, sa_sink_weight(M, sink));
 #pragma unroll
   for (int i = 0; i < VR; ++i) {
     const int dv = lane + 32 * i;
     if (dv < vdim) {
       const float gt = gate ? hy_sigmoid(gate[(size_t)t * ld_gate + (size_t)h * vdim + dv]) : 1.f;
-      out[(size_t)t * ldo + (size_t)h * vdim + dv] = from_f32<TO>(acc[i] * inv * gt);
+      out[(size_t)t * ldo + (size_t)h * vdim + dv] = from_f32<TO>(fmaf(e, acc[i], 0.f) * inv * gt);
     }
   }
 }
@@ -230,12 +237,13 @@ __global__ void sink_attention_merge_kernel(const float* ws, int splits, const f
   if (idx >= (long long)n * H) return;
   const int t = (int)(idx / H), h = (int)(idx - (long long)t * H);
   const float* w = ws + (size_t)idx * splits * (vdim + 2);
-  float M = sink ? 0.f : -INFINITY;
+  float M = -INFINITY;
   for (int s = 0; s < splits; ++s) M = fmaxf(M, w[(size_t)s * (vdim + 2)]);
-  float L = sink ? expf(0.f - M) : 0.f;
+  M = sa_top(M, sink);
+  float L = sa_sink_weight(M, sink);
   for (int s = 0; s < splits; ++s) {
     const float ms = w[(size_t)s * (vdim + 2)];
-    if (ms > -INFINITY) L += expf(ms - M) * w[(size_t)s * (vdim + 2) + 1];
+    if (ms > -INFINITY) L = fmaf(expf(ms - M), w[(size_t)s * (vdim + 2) + 1], L);
   }
   const float inv = 1.0f / L;
   for (int dv = lane; dv < vdim; dv += 32) {
@@ -265,12 +273,13 @@ GB_API int gb_sink_attention_chunks(int n, int H, int G, int window, int max_ctx
   int wanted = 592 / (blocks > 0 ? blocks : 1);
   if (wanted > 64) wanted = 64;
   const int span = window > 0 ? window : (max_ctx > 0 ? max_ctx : 1);
-  if (wanted <= 1 || span <= 2 * SA_KT) { *chunk_out = span; return 1; }
+  // (with a window the cut depends on the launch's sizes only, not on how long the contexts are)
+  if (wanted <= 1 || (window > 0 && span <= SA_KT)) { *chunk_out = span; return 1; }
   int chunk;
   if (window > 0) {
     chunk = SA_KT * gb_div_up(gb_div_up(span, wanted), SA_KT);
   } else {
-    chunk = 128;
+    chunk = 256;
     while (gb_div_up(span, chunk) > 2 * wanted) chunk *= 2;
   }
   *chunk_out = chunk;

@@ -206,7 +206,8 @@ class PartHarness:
     into portions.  ``feed(request, h)`` runs the next tokens of a request and returns the mixer's
     output for them (float32)."""
 
-    def __init__(self, part, n_pages=64, page_size=16, n_slots=3, max_context=1024, guard=True):
+    def __init__(self, part, n_pages=64, page_size=16, n_slots=3, max_context=1024, guard=True, fill=float("nan")):
+        self.fill = fill            # what the output rows hold before the part runs (0 for a part that ADDS its output)
         from gibbs_b200.cache import CacheManager
         from gibbs_b200.engine.step import StepBuilder
         self.part, self.rt = part, part.rt
@@ -227,7 +228,7 @@ class PartHarness:
         self.cache.reserve_all([(rc, rc.length + len(e.tokens)) for rc, e in zip(rcs, entries)])
         step, caches = self.builder.build(entries, rcs)
         h = torch.cat(list(portions.values()), 0).to(self.rt.device, self.rt.dtype).contiguous()
-        out = torch.full((h.shape[0], self.part.hidden), float("nan"), dtype=torch.float32, device=self.rt.device)
+        out = torch.full((h.shape[0], self.part.hidden), self.fill, dtype=torch.float32, device=self.rt.device)
         self.part.forward(h, out, step, caches[0])
         torch.cuda.synchronize()
         for rc, e in zip(rcs, entries):
