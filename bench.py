@@ -70,21 +70,51 @@ def potivik_shape(size: str) -> dict:
             "token_side": {"dim": side}, "layers": layers}
 
 
+def petelix_shape(size: str) -> dict:
+    """Layer sizes that resemble a real model's, for the Petelix design: attention layers with routed experts,
+    every second layer reading the keys and values of the layer before it."""
+    if size == "1k":
+        d, vocab = 1024, 32768
+        att = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 32, "scale": 0.125, "softcap": 30.0, "mask": {"size": 512},
+               "rot": {"base": 500000.0, "dims": 32}}
+        moe = {"kind": "moe", "router": {"experts": 14, "identity": 2, "top": 2, "groups": {"count": 4, "keep": 2}},
+               "expert": {"ff": 1024}}
+    else:
+        d, vocab = 2048, 65536
+        att = {"heads": 32, "kv_heads": 8, "dim": 64, "vdim": 64, "scale": 0.125, "softcap": 30.0, "mask": {"size": 1024},
+               "rot": {"base": 500000.0, "dims": 32}}
+        moe = {"kind": "moe", "router": {"experts": 30, "identity": 2, "top": 4, "groups": {"count": 4, "keep": 2}},
+               "expert": {"ff": 1024}}
+    layers = [{"type": "attention", "mixer": dict(att, **({"kv_from": i - 1} if i % 2 else {})), "mlp": moe} for i in range(8)]
+    return {"architecture": "Petelix", "vocab": vocab, "width": d, "norm": {"eps": 1e-6}, "embedding": {"scale": 8.0},
+            "layers": layers}
+
+
 def potivik_workload(a):
     """Prompt and decode throughput of the Potivik design at two sizes (random weights), beside an LFM2
     model of equal width, depth and feed-forward width, with the time per kind of operation of one
-    prompt step and one decode step (the walker's timing mode).  One JSON line per model and size."""
+    prompt step and one decode step (the walker's timing mode).  One JSON line per model and size.
+    'petelix': the same for the Petelix design, beside an LFM2 model whose layers are all attention layers
+    and whose feed-forward is as wide as the experts a token uses."""
     import torch
     from gibbs_b200 import Engine, Lfm2Config, parse_config, random_model
     from gibbs_b200.engine import benchmark as B
     prompt, batch, ctx = 2048, 8, 1024
     for size in (a.size.split(",") if a.size else ["1k", "2k"]):
-        pot = potivik_shape(size)
-        d = pot["width"]
-        twin = dict(LFM2_1P2B, hidden_size=d, num_hidden_layers=8, num_attention_heads=d // 64, num_key_value_heads=d // 256,
-                    head_dim=64, vocab_size=pot["vocab"], intermediate_size=4 * d, block_auto_adjust_ff_dim=False,
-                    full_attn_idxs=[1, 3, 5, 7], max_position_embeddings=4096)
-        for name, conf in (("Potivik", parse_config(pot)), ("LFM2 of equal size", Lfm2Config.from_dict(twin))):
+        if a.workload == "petelix":
+            pot = petelix_shape(size)
+            d, m, r = pot["width"], pot["layers"][0]["mixer"], pot["layers"][0]["mlp"]["router"]
+            twin = dict(LFM2_1P2B, hidden_size=d, num_hidden_layers=8, num_attention_heads=m["heads"],
+                        num_key_value_heads=m["kv_heads"], head_dim=m["dim"], vocab_size=pot["vocab"],
+                        intermediate_size=r["top"] * pot["layers"][0]["mlp"]["expert"]["ff"], block_auto_adjust_ff_dim=False,
+                        full_attn_idxs=list(range(8)), max_position_embeddings=4096)
+        else:
+            pot = potivik_shape(size)
+            d = pot["width"]
+            twin = dict(LFM2_1P2B, hidden_size=d, num_hidden_layers=8, num_attention_heads=d // 64, num_key_value_heads=d // 256,
+                        head_dim=64, vocab_size=pot["vocab"], intermediate_size=4 * d, block_auto_adjust_ff_dim=False,
+                        full_attn_idxs=[1, 3, 5, 7], max_position_embeddings=4096)
+        for name, conf in ((pot["architecture"], parse_config(pot)), ("LFM2 of equal size", Lfm2Config.from_dict(twin))):
             model = random_model(conf, SEED, dtype="bfloat16", device="cuda:0", stored_dtype=torch.bfloat16)
             eng = Engine(model, n_pages=(batch + 1) * (4096 // 16), page_size=16, max_requests=batch, max_step_tokens=prompt,
                          max_context=4096)
@@ -175,10 +205,10 @@ def main():
                     help="float32: the engine's true 32-bit twin on the same (bfloat16-rounded) weights; "
                          "with --only prefill or --only decode (the benchmark line itself is bfloat16)")
     ap.add_argument("--skip-points", action="store_true", help="skip batch 1 and 64")
-    ap.add_argument("--workload", choices=["serve700m", "long2p6b", "sweep", "potivik"], default=None,
-                    help="run one of the other workloads instead (prints its own JSON lines); 'potivik': the Potivik "
+    ap.add_argument("--workload", choices=["serve700m", "long2p6b", "sweep", "potivik", "petelix"], default=None,
+                    help="run one of the other workloads instead (prints its own JSON lines); 'potivik' / 'petelix': that "
                          "design at layer sizes of a real model, beside an LFM2 model of equal size")
-    ap.add_argument("--size", default=None, help="with --workload potivik: '1k', '2k' or both with a comma (default both)")
+    ap.add_argument("--size", default=None, help="with --workload potivik or petelix: '1k', '2k' or both with a comma (default both)")
     ap.add_argument("--prompt-tokens", type=int, default=None,
                     help="with --only prefill / prefill-timeline / products: another prompt length than 2,048")
     ap.add_argument("--only", default=None,
@@ -201,7 +231,7 @@ def main():
     from gibbs_b200 import Generator, Lfm2Config, random_model
     from gibbs_b200.engine import benchmark as B
 
-    if a.workload == "potivik":
+    if a.workload in ("potivik", "petelix"):
         return potivik_workload(a)
     if a.workload:
         return other_workload(a)

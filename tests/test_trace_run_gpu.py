@@ -147,3 +147,35 @@ def test_trace_run_potivik_with_and_without_dependent_launch(tmp_path):
     for rid in results["serial"]:
         for p in results["serial"][rid]:
             assert np.array_equal(results["serial"][rid][p], results["overlapped"][rid][p]), (rid, p)
+
+
+def test_trace_run_petelix_with_and_without_dependent_launch(tmp_path):
+    """The Petelix design through the same runner: a model folder on disk (bfloat16 weights), float32
+    compute, mixed steps with sparse wants in a pool that makes pages go round (two groups of pages:
+    one windowed, one that keeps everything); the runs with and without programmatic dependent launch
+    agree with the plain implementation and with each other to the bit."""
+    import plain_petelix
+    from petelix_helpers import CFG_A, make_weights
+    from potivik_helpers import rel_rows, write_model
+    W = make_weights(CFG_A, 31)
+    folder = write_model(tmp_path / "petelix_a", CFG_A, W)
+    vocab = CFG_A["vocab"]
+    reqs = {f"q{i}": random_ids(60 + i, n, vocab) for i, n in enumerate([70, 45, 130, 1, 64, 20])}
+    steps = trace_mixed(reqs, capacity_tokens=320, max_live=4, seed=6)
+    for k, s in enumerate(steps):
+        for e in s["entries"]:
+            e["want"] = [] if k % 5 == 4 else [w for w in e["want"] if (w + k) % 3]
+    want = {rid: plain_petelix.forward(CFG_A, W, ids).numpy() for rid, ids in reqs.items()}
+    results = {}
+    for mode, env in (("serial", {"GIBBS_B200_PDL": "0"}), ("overlapped", {"GIBBS_B200_PDL": "1"})):
+        out = tmp_path / f"out_{mode}"
+        _run(folder, "float32", steps, out, max_tokens=320, env=env)
+        got = results[mode] = _collect(steps, out, vocab)
+        for rid in reqs:
+            rows = sorted(got.get(rid, {}))
+            if rows:
+                e = rel_rows(np.stack([got[rid][p] for p in rows]), want[rid][rows])
+                assert e.max() <= 2e-4, f"{mode}, {rid}: place {rows[int(e.argmax())]} differs by {e.max():.3g}"
+    for rid in results["serial"]:
+        for p in results["serial"][rid]:
+            assert np.array_equal(results["serial"][rid][p], results["overlapped"][rid][p]), (rid, p)
