@@ -31,7 +31,7 @@ LIBRARIES = {
     "runtime": ["errors.cu", "step_plan.cu"],
     # layer norms, clamped gated units, latent and gated attention, state-space recurrences, routed experts: every entry
     # point has the signature of a step-plan operation (hybrid.cuh)
-    "hybrid": ["errors.cu", "norms.cu", "latent_attention.cu", "gated_attention.cu", "ssm.cu", "moe.cu", "moe_tc.cu"],
+    "hybrid": ["errors.cu", "norms.cu", "latent_attention.cu", "gated_attention.cu", "gated_attention_tc.cu", "ssm.cu", "moe.cu", "moe_tc.cu"],
 }
 
 NVCC_FLAGS = [

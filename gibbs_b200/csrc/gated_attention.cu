@@ -264,6 +264,20 @@ constexpr int SA_WS_ROWS = 1 << 16;
 // Rows of (vdim + 2) floats a launch's partial results may need, whatever its sizes.
 GB_API int gb_sink_attention_workspace_rows() { return SA_WS_ROWS; }
 
+// The merge of chunks, for this file's kernel and for the tensor-core one (gated_attention_tc.cu).
+int gb_sink_attention_merge(const float* ws, int splits, const float* gate, long long ld_gate, void* out, int out_bf16,
+                            long long ldo, int n, int H, int vdim, int sink, cudaStream_t stream) {
+  const dim3 mgrid(gb_div_up((long long)n * H, 4));
+  if (out_bf16)
+    gb_launch(sink_attention_merge_kernel<bf16>, mgrid, dim3(128), 0, stream, ws, splits, gate, ld_gate, (bf16*)out, ldo, n,
+              H, vdim, sink);
+  else
+    gb_launch(sink_attention_merge_kernel<float>, mgrid, dim3(128), 0, stream, ws, splits, gate, ld_gate, (float*)out, ldo,
+              n, H, vdim, sink);
+  GB_CHECK_LAUNCH("sink_attention_merge");
+  return 1;
+}
+
 // How the visible keys of a launch are cut into chunks of whole key tiles: (chunks, keys per chunk).  Few
 // tokens (decoding) get many chunks, so that the GPU is occupied.  Chunks lie at fixed distances from the
 // first visible key, so a chunk's partial result does not depend on how many chunks there are.
@@ -378,13 +392,7 @@ GB_OP(gb_op_sink_attention) {
 #undef SA
   GB_CHECK_LAUNCH("sink_attention");
   if (splits == 1) return 1;
-  const dim3 mgrid(gb_div_up((long long)n * H, 4));
-  if (ob)
-    gb_launch(sink_attention_merge_kernel<bf16>, mgrid, dim3(128), 0, ctx->stream, ws, splits, op_ptr<const float>(a[9]),
-              a[10], op_ptr<bf16>(a[11]), a[12], n, H, vdim, sink);
-  else
-    gb_launch(sink_attention_merge_kernel<float>, mgrid, dim3(128), 0, ctx->stream, ws, splits,
-              op_ptr<const float>(a[9]), a[10], op_ptr<float>(a[11]), a[12], n, H, vdim, sink);
-  GB_CHECK_LAUNCH("sink_attention_merge");
-  return 2;
+  const int rc = gb_sink_attention_merge(ws, splits, op_ptr<const float>(a[9]), a[10], op_ptr<void>(a[11]), ob ? 1 : 0, a[12],
+                                         n, H, vdim, sink, ctx->stream);
+  return rc < 0 ? rc : 2;
 }

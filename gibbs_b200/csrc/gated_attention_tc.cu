@@ -1,0 +1,359 @@
+// The attention of gated_attention.cu on the tensor cores, for bfloat16 queries and pages: keys of DK and
+// values of DV entries (multiples of 16, which may differ), sliding window, soft cap, sink, output gate.
+//
+// The rows of a CTA's tile are (token, query head of one kv group) pairs of consecutive tokens of ONE
+// request, so the keys and values of a kv head are read from the pages once for all the query heads that
+// share them.  A CTA walks the visible keys in tiles of 64 positions (cp.async into two buffers, looked up
+// page by page), computes S = Q K^T and O += P V with mma.sync m16n8k16, and keeps scores, soft cap,
+// exponentials, maxima and sums in 32-bit.  The weights enter the second product as TWO bfloat16 terms
+// (p = hi + lo, O += hi V + lo V), which keeps 16 bits of every weight.  With several chunks of keys
+// (blockIdx.z) a CTA leaves (maximum, sum, weighted sum) per row for the merge kernel of gated_attention.cu.
+#include <cuda_bf16.h>
+
+#include "hybrid.cuh"
+
+namespace {
+
+enum { STATUS_BAD_PAGE_READ = 2 };
+constexpr int TC_KT = 64, TC_ROWS = 64, TC_THREADS = 128;
+
+__device__ __forceinline__ void cp16_zfill(void* smem, const void* gmem, bool valid) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;               // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t* r, const void* smem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t* r, const void* smem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// tanh(x) = 1 - 2 / (exp(2x) + 1) with the hardware's exponential and reciprocal: a few 2^-23 of 1
+__device__ __forceinline__ float tc_tanh(float x) { return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f); }
+// p as two bfloat16 terms, packed for two neighbouring columns
+__device__ __forceinline__ void split2(float x, float y, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+  const float2 hf = __bfloat1622float2(h);
+  const __nv_bfloat162 l = __floats2bfloat162_rn(x - hf.x, y - hf.y);
+  hi = *reinterpret_cast<const uint32_t*>(&h);
+  lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+
+struct TcParams {
+  const bf16* q; long long ldq;
+  const bf16* k_pages; const bf16* v_pages;
+  const int* block_table; int bt_stride, page_size, n_pages;
+  const int* tok_req; const int* tok_pos; const int* q_start;
+  const float* gate; long long ld_gate;
+  bf16* out; long long ldo;
+  int N, R, H, G, tokens_per_tile;
+  float scale, softcap;
+  int window, sink, splits, chunk;
+  float* ws; int* status;
+};
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(TC_THREADS) sink_attention_tc_kernel(TcParams p) {
+  constexpr int KS = DK + 8, VS = DV + 8;                    // elements between rows in shared memory
+  extern __shared__ __align__(16) unsigned char tc_smem[];
+  bf16* Qs = reinterpret_cast<bf16*>(tc_smem);               // [TC_ROWS][KS]
+  bf16* Ks = Qs + TC_ROWS * KS;                              // [2][TC_KT][KS]
+  bf16* Vs = Ks + 2 * TC_KT * KS;                            // [2][TC_KT][VS]
+  pdl_trigger();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int group = p.H / p.G, g = blockIdx.y, tpt = p.tokens_per_tile;
+  // this CTA's request and first token: the tiles of the step's requests, one request after the other
+  int tile = blockIdx.x, t0 = -1, n_tok = 0;
+  for (int r = 0; r < p.R; ++r) {
+    const int qs = p.q_start[r], qe = r + 1 < p.R ? p.q_start[r + 1] : p.N;
+    const int tiles = (qe - qs + tpt - 1) / tpt;
+    if (tile < tiles) {
+      t0 = qs + tile * tpt;
+      n_tok = min(tpt, qe - t0);
+      break;
+    }
+    tile -= tiles;
+  }
+  if (t0 < 0) return;
+  const int pos0 = p.tok_pos[t0];
+  const int* table = p.block_table + (size_t)p.tok_req[t0] * p.bt_stride;
+  const int n_rows = n_tok * group;
+  const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int k_begin = p.splits > 1 ? lo + (int)blockIdx.z * p.chunk : lo;
+  const int k_end = p.splits > 1 ? min(pos0 + n_tok - 1, k_begin + p.chunk - 1) : pos0 + n_tok - 1;
+  const int n_tiles = k_end >= k_begin ? (k_end - k_begin) / TC_KT + 1 : 0;
+
+  auto load_kv = [&](int it, int buf) {
+    const int k0 = k_begin + it * TC_KT;
+    bf16* kd = Ks + buf * TC_KT * KS;
+    bf16* vd = Vs + buf * TC_KT * VS;
+    for (int c = tid; c < TC_KT * (DK / 8 + DV / 8); c += TC_THREADS) {
+      const int j = c / (DK / 8 + DV / 8), part = c - j * (DK / 8 + DV / 8);
+      const int kp = k0 + j;
+      long long row = -1;
+      if (kp <= k_end) {
+        const int page = table[kp / p.page_size];
+        if (page < 0 || page >= p.n_pages) atomicExch(p.status, STATUS_BAD_PAGE_READ);
+        else row = ((long long)page * p.G + g) * p.page_size + kp % p.page_size;
+      }
+      if (part < DK / 8)
+        cp16_zfill(kd + j * KS + part * 8, p.k_pages + (row < 0 ? 0 : row) * DK + part * 8, row >= 0);
+      else
+        cp16_zfill(vd + j * VS + (part - DK / 8) * 8, p.v_pages + (row < 0 ? 0 : row) * DV + (part - DK / 8) * 8, row >= 0);
+    }
+    cp_commit();
+  };
+
+  pdl_wait();
+  // queries of the tile: row R is (token t0 + R / group, head g * group + R % group)
+  for (int c = tid; c < TC_ROWS * (DK / 8); c += TC_THREADS) {
+    const int R = c / (DK / 8), part = c - R * (DK / 8);
+    const bool valid = R < n_rows;
+    const int tt = valid ? R / group : 0, hh = valid ? R - tt * group : 0;
+    cp16_zfill(Qs + R * KS + part * 8, p.q + (size_t)(t0 + tt) * p.ldq + (size_t)(g * group + hh) * DK + part * 8, valid);
+  }
+  cp_commit();
+  if (n_tiles > 0) load_kv(0, 0);
+  cp_wait<0>();
+  __syncthreads();
+
+  const bool warp_live = warp * 16 < n_rows;
+  uint32_t qf[DK / 16][4];
+  if (warp_live) {
+#pragma unroll
+    for (int kk = 0; kk < DK / 16; ++kk)
+      ldsm_x4(qf[kk], Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KS + kk * 16 + (lane >> 4) * 8);
+  }
+  // this thread's two rows and their positions
+  const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+  const int pos_lo = r_lo < n_rows ? pos0 + r_lo / group : -1, pos_hi = r_hi < n_rows ? pos0 + r_hi / group : -1;
+  const int first_lo = p.window > 0 ? pos_lo - p.window + 1 : 0, first_hi = p.window > 0 ? pos_hi - p.window + 1 : 0;
+  float o[DV / 8][4];
+#pragma unroll
+  for (int n = 0; n < DV / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+  const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
+
+  for (int it = 0; it < n_tiles; ++it) {
+    if (it + 1 < n_tiles) {
+      load_kv(it + 1, (it + 1) & 1);
+      cp_wait<1>();
+    } else {
+      cp_wait<0>();
+    }
+    __syncthreads();
+    if (warp_live) {
+      const bf16* kb = Ks + (it & 1) * TC_KT * KS;
+      const bf16* vb = Vs + (it & 1) * TC_KT * VS;
+      const int k0 = k_begin + it * TC_KT;
+      float s[TC_KT / 8][4];
+#pragma unroll
+      for (int n = 0; n < TC_KT / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < DK / 16; ++kk) {
+#pragma unroll
+        for (int n2 = 0; n2 < TC_KT / 16; ++n2) {
+          uint32_t b[4];
+          ldsm_x4(b, kb + (n2 * 16 + (lane & 7) + (lane >> 4) * 8) * KS + kk * 16 + ((lane >> 3) & 1) * 8);
+          mma16816(s[2 * n2], qf[kk], b[0], b[1]);
+          mma16816(s[2 * n2 + 1], qf[kk], b[2], b[3]);
+        }
+      }
+      // scale, soft cap, mask; the rows' maxima
+      float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+      for (int n = 0; n < TC_KT / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int kp = k0 + n * 8 + (lane & 3) * 2 + (e & 1);
+          const int pos = e < 2 ? pos_lo : pos_hi, first = e < 2 ? first_lo : first_hi;
+          float v = s[n][e] * p.scale;
+          if (p.softcap > 0.f) v = p.softcap * tc_tanh(v * inv_cap);
+          if (kp > pos || kp < first || kp > k_end) v = -INFINITY;
+          s[n][e] = v;
+          if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
+        }
+      }
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+      const float use_lo = mn_lo == -INFINITY ? 0.f : mn_lo, use_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+      const float c_lo = __expf(m_lo - use_lo), c_hi = __expf(m_hi - use_hi);   // 0 while the row has seen nothing
+      m_lo = mn_lo; m_hi = mn_hi;
+      float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+      for (int n = 0; n < TC_KT / 8; ++n) {
+        s[n][0] = __expf(s[n][0] - use_lo); s[n][1] = __expf(s[n][1] - use_lo);
+        s[n][2] = __expf(s[n][2] - use_hi); s[n][3] = __expf(s[n][3] - use_hi);
+        sum_lo += s[n][0] + s[n][1];
+        sum_hi += s[n][2] + s[n][3];
+      }
+      sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
+      sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
+      sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1);
+      sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 2);
+      l_lo = l_lo * c_lo + sum_lo;
+      l_hi = l_hi * c_hi + sum_hi;
+#pragma unroll
+      for (int n = 0; n < DV / 8; ++n) {
+        o[n][0] *= c_lo; o[n][1] *= c_lo; o[n][2] *= c_hi; o[n][3] *= c_hi;
+      }
+#pragma unroll
+      for (int j = 0; j < TC_KT / 16; ++j) {
+        uint32_t ph[4], pl[4];
+        split2(s[2 * j][0], s[2 * j][1], ph[0], pl[0]);
+        split2(s[2 * j][2], s[2 * j][3], ph[1], pl[1]);
+        split2(s[2 * j + 1][0], s[2 * j + 1][1], ph[2], pl[2]);
+        split2(s[2 * j + 1][2], s[2 * j + 1][3], ph[3], pl[3]);
+#pragma unroll
+        for (int n2 = 0; n2 < DV / 16; ++n2) {
+          uint32_t b[4];
+          ldsm_x4_t(b, vb + (j * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + n2 * 16 + (lane >> 4) * 8);
+          mma16816(o[2 * n2], ph, b[0], b[1]);
+          mma16816(o[2 * n2 + 1], ph, b[2], b[3]);
+          mma16816(o[2 * n2], pl, b[0], b[1]);
+          mma16816(o[2 * n2 + 1], pl, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();                                         // the buffer is free for the tile after the next
+  }
+  if (!warp_live) return;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int R = half ? r_hi : r_lo;
+    if (R >= n_rows) continue;
+    const int tt = R / group, h = g * group + (R - tt * group), t = t0 + tt;
+    const float m = half ? m_hi : m_lo, l = half ? l_hi : l_lo;
+    if (p.splits > 1) {
+      float* w = p.ws + (((size_t)t * p.H + h) * p.splits + blockIdx.z) * (DV + 2);
+      if ((lane & 3) == 0) { w[0] = m; w[1] = l; }
+#pragma unroll
+      for (int n = 0; n < DV / 8; ++n) {
+        w[2 + n * 8 + (lane & 3) * 2] = o[n][2 * half];
+        w[2 + n * 8 + (lane & 3) * 2 + 1] = o[n][2 * half + 1];
+      }
+      continue;
+    }
+    // (the same arithmetic as the merge of chunks: one chunk, and the sink)
+    const float M = p.sink ? fmaxf(m, 0.f) : m;
+    const float e = expf(m - M);
+    const float inv = 1.0f / fmaf(e, l, p.sink ? expf(0.f - M) : 0.f);
+    const float* gt = p.gate ? p.gate + (size_t)t * p.ld_gate + (size_t)h * DV : nullptr;
+    bf16* dst = p.out + (size_t)t * p.ldo + (size_t)h * DV;
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n) {
+      const int d = n * 8 + (lane & 3) * 2;
+      const float g0 = gt ? hy_sigmoid(gt[d]) : 1.f, g1 = gt ? hy_sigmoid(gt[d + 1]) : 1.f;
+      *reinterpret_cast<__nv_bfloat162*>(dst + d) =
+          __floats2bfloat162_rn(fmaf(e, o[n][2 * half], 0.f) * inv * g0, fmaf(e, o[n][2 * half + 1], 0.f) * inv * g1);
+    }
+  }
+}
+
+template <int DK, int DV>
+int launch_tc(const TcParams& p, dim3 grid, cudaStream_t stream) {
+  constexpr int smem = (TC_ROWS * (DK + 8) + 2 * TC_KT * (DK + 8) + 2 * TC_KT * (DV + 8)) * 2;
+  static bool raised = false;            // once per size, before any stream capture replays the launch
+  if (!raised && smem > 48 * 1024) {
+    GB_CUDA(cudaFuncSetAttribute(sink_attention_tc_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    raised = true;
+  }
+  gb_launch(sink_attention_tc_kernel<DK, DV>, grid, dim3(TC_THREADS), smem, stream, p);
+  GB_CHECK_LAUNCH("sink_attention_tc");
+  return 1;
+}
+
+}  // namespace
+
+// (gated_attention.cu)
+int gb_sink_attention_merge(const float* ws, int splits, const float* gate, long long ld_gate, void* out, int out_bf16,
+                            long long ldo, int n, int H, int vdim, int sink, cudaStream_t stream);
+extern "C" int gb_sink_attention_workspace_rows();
+
+// Whether the tensor-core kernel takes these sizes (keys and values of 32 to 128 entries in steps of 32, up to
+// 64 query heads a kv head, rows that 16-byte copies can address).
+GB_API int gb_sink_attention_tc_supported(int heads, int kv_heads, int dim, int vdim) {
+  if (kv_heads <= 0 || heads % kv_heads || heads / kv_heads > TC_ROWS) return 0;
+  const bool dk = dim == 32 || dim == 64 || dim == 96 || dim == 128;
+  const bool dv = vdim == 32 || vdim == 64 || vdim == 96 || vdim == 128;
+  return dk && dv;
+}
+
+// a0 q [tokens, heads * dim] (bf16), a1 key pages, a2 value pages (bf16), a3 block table, a4 its entries per request,
+// a5 page size, a6 number of pages, a7 token -> request, a8 token -> position, a9 gate logits (f32) or 0, a10 their row
+// stride, a11 out [tokens, heads * vdim] (bf16), a12 its row stride, a13 tokens, a14 heads, a15 kv heads, a16 dim,
+// a17 vdim, a18 window (0: every earlier position), a19 longest context of the step (an upper bound will do), a20
+// workspace for partial results (gb_sink_attention_workspace_rows() rows of vdim + 2 floats) or 0, a21 requests, a22
+// row of each request's first token [requests]; flags bit 0: the softmax has a sink; f0 scale, f1 soft cap (0: none)
+GB_OP(gb_op_sink_attention_tc) {
+  const int n = (int)a[13], H = (int)a[14], G = (int)a[15], dim = (int)a[16], vdim = (int)a[17], R = (int)a[21];
+  if (n <= 0 || R <= 0) return 0;
+  if (!gb_sink_attention_tc_supported(H, G, dim, vdim))
+    GB_FAIL(GB_ERR_ARG, "sink_attention_tc: %d heads over %d kv heads of %d / %d entries are not built", H, G, dim, vdim);
+  if ((a[0] & 15) || (a[1] & 15) || (a[2] & 15) || (a[11] & 3) || (a[12] & 1))
+    GB_FAIL(GB_ERR_ARG, "sink_attention_tc: operands are not aligned for 16-byte copies");
+  const int group = H / G;
+  TcParams p;
+  p.q = op_ptr<const bf16>(a[0]); p.ldq = (long long)H * dim;
+  p.k_pages = op_ptr<const bf16>(a[1]); p.v_pages = op_ptr<const bf16>(a[2]);
+  p.block_table = op_ptr<const int>(a[3]); p.bt_stride = (int)a[4]; p.page_size = (int)a[5]; p.n_pages = (int)a[6];
+  p.tok_req = op_ptr<const int>(a[7]); p.tok_pos = op_ptr<const int>(a[8]); p.q_start = op_ptr<const int>(a[22]);
+  p.gate = op_ptr<const float>(a[9]); p.ld_gate = a[10];
+  p.out = op_ptr<bf16>(a[11]); p.ldo = a[12];
+  p.N = n; p.R = R; p.H = H; p.G = G; p.tokens_per_tile = TC_ROWS / group;
+  p.scale = (float)f[0]; p.softcap = (float)f[1];
+  p.window = (int)a[18]; p.sink = flags & 1;
+  p.ws = op_ptr<float>(a[20]); p.status = ctx->status;
+  // at most this many tiles: every request may end with a partial one
+  const int tiles = gb_div_up(n, p.tokens_per_tile) + R;
+  // chunks of keys when the tiles alone leave the GPU idle (decoding); whole key tiles, at fixed distances from the
+  // first visible key; with a window the cut depends on the launch's sizes only
+  const int span = p.window > 0 ? p.window + p.tokens_per_tile : (a[19] > 0 ? (int)a[19] : 1);
+  int wanted = 296 / (tiles * G);
+  if (wanted > 32) wanted = 32;
+  p.splits = 1; p.chunk = span;
+  if (wanted > 1 && p.ws != nullptr && !(p.window > 0 && span <= TC_KT)) {
+    int chunk;
+    if (p.window > 0) {
+      chunk = TC_KT * gb_div_up(gb_div_up(span, wanted), TC_KT);
+    } else {
+      chunk = 256;
+      while (gb_div_up(span, chunk) > 2 * wanted) chunk *= 2;
+    }
+    const int splits = gb_div_up(span, chunk);
+    if (splits > 1 && (long long)n * H * splits <= gb_sink_attention_workspace_rows()) {
+      p.splits = splits;
+      p.chunk = chunk;
+    }
+  }
+  const dim3 grid(tiles, G, p.splits);
+  int rc;
+#define TC(DK, DV) rc = launch_tc<DK, DV>(p, grid, ctx->stream)
+#define TC_DV(DK)                                                                                    \
+  do {                                                                                               \
+    if (vdim == 32) TC(DK, 32); else if (vdim == 64) TC(DK, 64); else if (vdim == 96) TC(DK, 96); else TC(DK, 128); \
+  } while (0)
+  if (dim == 32) TC_DV(32); else if (dim == 64) TC_DV(64); else if (dim == 96) TC_DV(96); else TC_DV(128);
+#undef TC_DV
+#undef TC
+  if (rc < 0) return rc;
+  if (p.splits == 1) return 1;
+  rc = gb_sink_attention_merge(p.ws, p.splits, p.gate, p.ld_gate, p.out, 1, p.ldo, n, H, vdim, p.sink, ctx->stream);
+  return rc < 0 ? rc : 2;
+}

@@ -1,5 +1,5 @@
 """Bindings of the "hybrid" kernel library (csrc/norms.cu, latent_attention.cu,
-gated_attention.cu, ssm.cu, moe.cu): layer norms, clamped gated units, latent
+gated_attention.cu, gated_attention_tc.cu, ssm.cu, moe.cu): layer norms, clamped gated units, latent
 attention, gated attention with a sink, state-space recurrences and routed experts.
 
 Every operation of that library has the signature of a step-plan operation,
@@ -22,7 +22,7 @@ LIBRARY = "hybrid"
 OPERATIONS = ("row_norm", "norm_add", "clamped_glu", "gelu_mul_rows", "gated_group_norm", "causal_conv_silu",
               "ssm_scan", "latent_prep", "head_linear", "latent_attention", "moe_route", "moe_sort", "moe_gather",
               "moe_experts", "moe_experts_tc", "moe_combine", "moe_route_grouped", "moe_combine_weighted",
-              "embed_scaled", "qk_prep", "sink_attention")
+              "embed_scaled", "qk_prep", "sink_attention", "sink_attention_tc")
 
 NORM_LAYER, NORM_RMS = 0, 1
 

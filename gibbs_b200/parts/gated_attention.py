@@ -21,6 +21,8 @@ input product writes 32-bit values, pages hold the compute dtype.
 """
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import torch
 
@@ -34,6 +36,15 @@ from .runner import Eager, Planned, Runner, keep
 def _workspace_rows() -> int:
     from ..ops.library import library
     return int(library(hybrid.LIBRARY).gb_sink_attention_workspace_rows())
+
+
+def _tensor_cores_take(heads: int, kv_heads: int, dim: int, vdim: int) -> bool:
+    from ..ops.library import library
+    return bool(library(hybrid.LIBRARY).gb_sink_attention_tc_supported(heads, kv_heads, dim, vdim))
+
+
+# GIBBS_B200_GATED_ATTN_TC=0: the generic kernel also where the tensor-core kernel would run (for comparison runs)
+USE_TENSOR_CORES = os.environ.get("GIBBS_B200_GATED_ATTN_TC", "1") != "0"
 
 
 class GatedAttention(Mixer):
@@ -112,16 +123,25 @@ class GatedAttention(Mixer):
             raise RuntimeError(f"pages of {tuple(kp.shape[1:])} / {tuple(vp.shape[1:])} for {G} kv heads of {dim} / {vdim}")
         table, bt_stride = rn.table(kv)
         pages_bf16 = kp.dtype == torch.bfloat16
-        q = rn.buffer("ga_query", H * dim, torch.float32)
+        # bfloat16 pages and sizes the tensor-core kernel is built for: queries in bfloat16 as well
+        tc = pages_bf16 and self.rt.dtype == torch.bfloat16 and USE_TENSOR_CORES and _tensor_cores_take(H, G, dim, vdim)
+        q = rn.buffer("ga_query", H * dim, torch.bfloat16 if tc else torch.float32)
         write = not self.shares_kv
         rn.op("qk_prep", [fused.data_ptr(), fused.stride(0), self.k_col, self.v_col, keep(rn, self.q_gain),
                           keep(rn, self.k_gain), keep(rn, self.inv_freq), self.rot_dims, rn.tok_req, rn.tok_pos, table,
                           bt_stride, kv.page_size, keep(rn, kp) if write else 0, keep(rn, vp) if write else 0,
                           kp.shape[0], rn.N, H, G, dim, vdim, q.data_ptr()], [self.eps],
-              flags=(1 if self.whole_norm else 0) | (4 if pages_bf16 else 0))
+              flags=(1 if self.whole_norm else 0) | (2 if tc else 0) | (4 if pages_bf16 else 0))
         out = rn.buffer("ga_heads_out", H * vdim)
         ws = rn.buffer("ga_partial", vdim + 2, torch.float32, fixed_rows=_workspace_rows())
         gate = fused.data_ptr() + 4 * self.gate_col if self.gated else 0
+        if tc:
+            rn.op("sink_attention_tc", [q.data_ptr(), keep(rn, kp), keep(rn, vp), table, bt_stride, kv.page_size,
+                                        kp.shape[0], rn.tok_req, rn.tok_pos, gate, fused.stride(0), out.data_ptr(),
+                                        out.stride(0), rn.N, H, G, dim, vdim, self.window or 0, rn.max_context,
+                                        ws.data_ptr(), rn.R, rn.q_start], [self.scale, self.softcap],
+                  label="sink_attention", flags=1 if self.sink else 0)
+            return out
         rn.op("sink_attention", [q.data_ptr(), keep(rn, kp), keep(rn, vp), table, bt_stride, kv.page_size, kp.shape[0],
                                  rn.tok_req, rn.tok_pos, gate, fused.stride(0), out.data_ptr(), out.stride(0), rn.N, H, G,
                                  dim, vdim, self.window or 0, rn.max_context, ws.data_ptr()], [self.scale, self.softcap],

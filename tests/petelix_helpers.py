@@ -65,7 +65,20 @@ CFG_C = {
         {"type": "attention", "mixer": _att(5, 5, 6, 3, 0.5, rot=(10000.0, 6), kv_from=1), "mlp": _moe(7, 2, 20, groups=(7, 3))},
     ],
 }
-CONFIGS = {"A": (CFG_A, 21), "B": (CFG_B, 22), "C": (CFG_C, 23)}
+# D: sizes the tensor-core attention kernel is built for (keys and values of 32, 64, 96 and 128 entries, unequal), one,
+# two, three and sixteen query heads a kv head, with and without a window, a reader with a wider window
+CFG_D = {
+    "architecture": "Petelix", "vocab": 211, "width": 128, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
+    "layers": [
+        {"type": "attention", "mixer": _att(4, 2, 32, 64, 0.2, window=40, rot=(1000.0, 16), softcap=10.0),
+         "mlp": _moe(4, 2, 64, identity=2, groups=(3, 2))},
+        {"type": "attention", "mixer": _att(4, 2, 32, 64, 0.2, window=70, rot=(1000.0, 16), softcap=10.0, kv_from=0), "mlp": None},
+        {"type": "attention", "mixer": _att(6, 2, 96, 32, 0.12, rot=(10000.0, 96)), "mlp": _moe(3, 1, 128)},
+        {"type": "attention", "mixer": _att(16, 1, 64, 128, 0.15, window=100, rot=(500.0, 8), softcap=4.0), "mlp": None},
+        {"type": "attention", "mixer": _att(3, 3, 128, 96, 0.1, window=16), "mlp": _moe(2, 2, 64)},
+    ],
+}
+CONFIGS = {"A": (CFG_A, 21), "B": (CFG_B, 22), "C": (CFG_C, 23), "D": (CFG_D, 24)}
 
 
 def random_config(seed: int) -> dict:
@@ -82,8 +95,8 @@ def random_config(seed: int) -> dict:
                 m["rot"] = dict(o["rot"])
         else:
             G = rng.choice([1, 2, 3, 5])
-            dim = rng.choice([2, 4, 8, 16, 24, 40])
-            m = _att(G * rng.choice([1, 2, 4, 9]), G, dim, rng.choice([1, 3, 8, 16, 33, 64]), rng.choice([0.2, 0.35, 0.5]))
+            dim = rng.choice([2, 4, 8, 16, 24, 32, 40, 64])
+            m = _att(G * rng.choice([1, 2, 4, 9]), G, dim, rng.choice([1, 3, 8, 16, 32, 33, 64]), rng.choice([0.2, 0.35, 0.5]))
             if rng.random() < 0.8:
                 m["rot"] = {"base": rng.choice([10.0, 1000.0, 500000.0]), "dims": rng.choice(range(2, dim + 1, 2))}
             sources.append(i)

@@ -19,7 +19,7 @@ import torch
 
 import plain_petelix as plain
 from helpers import run_trace_on_engine, trace_mixed, trace_portions, trace_tail_decoded, trace_whole
-from petelix_helpers import (CFG_A, CFG_B, CFG_C, CONFIGS, attention_params, build, make_weights, random_config,
+from petelix_helpers import (CFG_A, CFG_B, CFG_C, CFG_D, CONFIGS, attention_params, build, make_weights, random_config,
                              routed_params)
 from potivik_helpers import PartHarness, ids_for, make_part, rel_rows
 
@@ -77,7 +77,8 @@ def _plain_mixer(h, W, m, eps):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("cfg,layer", [(CFG_A, 0), (CFG_A, 2), (CFG_B, 0), (CFG_B, 1), (CFG_C, 0), (CFG_C, 1)])
+@pytest.mark.parametrize("cfg,layer", [(CFG_A, 0), (CFG_A, 2), (CFG_B, 0), (CFG_B, 1), (CFG_C, 0), (CFG_C, 1),
+                                       (CFG_D, 0), (CFG_D, 2), (CFG_D, 3), (CFG_D, 4)])
 def test_attention_alone_whole_cut_and_decoded(cfg, layer, dtype):
     m, d, eps = cfg["layers"][layer]["mixer"], cfg["width"], cfg["norm"]["eps"]
     W = plain.sub(make_weights(cfg, 5), f"l{layer}.mix.")
@@ -142,11 +143,11 @@ def test_the_norm_is_over_the_whole_projection_and_the_cap_bends_large_scores(dt
     check_rows(hz.run_cut("a", h, [33, 2, 1]), want, dtype, what="unequal heads, capped scores")
 
 
-def _pointed_attention(window, T, hot_key, query, seed=7):
+def _pointed_attention(window, T, hot_key, query, vdim=8, seed=7):
     """Weights and inputs for which the query position's score against ``hot_key`` stands far above all
     others (when that key is visible), and whose values tell keys apart.  Keys read the input's first 64
     entries, queries its last 64: the query token's own key is an ordinary one."""
-    d, H, G, dim, vdim = 128, 2, 1, 64, 8
+    d, H, G, dim = 128, 2, 1, 64
     m = {"heads": H, "kv_heads": G, "dim": dim, "vdim": vdim, "scale": 1.0, "softcap": 100.0}
     if window:
         m["mask"] = {"size": window}
@@ -165,6 +166,7 @@ def _pointed_attention(window, T, hot_key, query, seed=7):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("decoded", [False, True])
+@pytest.mark.parametrize("vdim", [8, 32])                     # 32: in bfloat16 the tensor-core kernel runs
 @pytest.mark.parametrize("window,T,hot,query", [
     (40, 120, 60, 99),        # the oldest key the window keeps (99 - 60 = 39)
     (40, 120, 59, 99),        # the first one it has dropped
@@ -174,14 +176,16 @@ def _pointed_attention(window, T, hot_key, query, seed=7):
     (16, 120, 79, 95),
     (32, 120, 64, 95),        # a window of one key tile
     (32, 120, 63, 95),
+    (64, 200, 128, 191),      # ... of the tensor-core kernel's key tile
+    (64, 200, 127, 191),
     (None, 400, 3, 399),      # no window: a key hundreds of positions back
     (None, 400, 16, 399),     # ... at a page's first row
     (None, 400, 31, 399),     # ... at a key tile's last row
     (300, 400, 100, 399),     # a long window: far but inside
     (300, 400, 99, 399),      # ... and outside
 ])
-def test_attention_finds_the_one_key_that_matters(window, T, hot, query, decoded, dtype):
-    m, W, h = _pointed_attention(window, T, hot, query)
+def test_attention_finds_the_one_key_that_matters(window, T, hot, query, vdim, decoded, dtype):
+    m, W, h = _pointed_attention(window, T, hot, query, vdim)
     part = make_part("mixer", "gated_attention", attention_params(m, h.shape[1], 1e-5), W, DTYPES[dtype])
     want = _plain_mixer(h, W, m, 1e-5)
     visible = window is None or query - hot < window
@@ -189,7 +193,9 @@ def test_attention_finds_the_one_key_that_matters(window, T, hot, query, decoded
     got = hz.run_cut("r", h, [query - 10, 1] if decoded else [T])
     e = rel_rows(got, want)
     assert e[query] <= TOL[dtype], f"query row differs by {e[query]:.3g}"
-    assert e.max() <= TOL[dtype]
+    # (the other rows' scores are eight times as wide as a model's: in bfloat16 the rounding of keys and queries
+    # shows in their sharp softmax)
+    assert e.max() <= (TOL[dtype] if dtype == "float32" else 0.1)
     # the hot key's value dominates the output exactly when it is visible (gate logits are zero: sigmoid = 1/2)
     v_hot = (W["v"].double() @ h[hot].double()) * 0.5
     out_hot = W["o"].double() @ torch.cat([v_hot, v_hot])
@@ -300,7 +306,7 @@ def engine_for(model, n_pages=64, page_size=16, max_requests=4, cap=512, **kw):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole_decoded_and_cut_prompts_match_the_plain_implementation(name, dtype):
     cfg, model, reqs, truth = model_and_truth(name, dtype)
     eng = engine_for(model)
@@ -312,7 +318,7 @@ def test_whole_decoded_and_cut_prompts_match_the_plain_implementation(name, dtyp
             check_rows(got[rid], truth[rid], dtype, strict=False, what=f"{name} {what} {rid}")
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_layer_by_layer_in_float32(name):
     """The residual stream after every layer, through the parts' forward methods."""
     cfg, model, reqs, _ = model_and_truth(name, "float32")
@@ -342,7 +348,7 @@ def test_layer_by_layer_in_float32(name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_plan_and_forward_methods_give_the_same_bits(name, dtype):
     cfg, model, reqs, _ = model_and_truth(name, dtype)
     steps = trace_mixed(reqs, capacity_tokens=320, seed=3)
@@ -353,7 +359,7 @@ def test_plan_and_forward_methods_give_the_same_bits(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixed_batches_with_pages_used_again(name, dtype):
     """Up to three live requests in a pool that holds little more than the live ones, portions beside
     single tokens: against the plain implementation, and against each request run alone."""
@@ -461,3 +467,23 @@ def test_command_line_from_a_configuration_to_tokens(tmp_path, capsys):
     out = capsys.readouterr().out
     generated = [int(t) for t in out.split("Output:\n")[1].splitlines()[0].split(",")]
     assert len(generated) == 5 and generated[0] == top["ids"][0]
+
+
+@pytest.mark.parametrize("cfg,layer", [(CFG_D, 0), (CFG_D, 2), (CFG_D, 3), (CFG_D, 4)])
+def test_tensor_core_attention_against_the_generic_kernel(cfg, layer, monkeypatch):
+    """In bfloat16 the two kernels read the same pages; they differ by the rounding of the queries and of
+    the weights' second term only.  A long request, cut so that tiles hold a few rows and many."""
+    from gibbs_b200.parts import gated_attention as ga
+    m, d, eps = cfg["layers"][layer]["mixer"], cfg["width"], cfg["norm"]["eps"]
+    W = plain.sub(make_weights(cfg, 5), f"l{layer}.mix.")
+    T = 330
+    h = bf(torch.randn(T, d, generator=gen(8)))
+    want = _plain_mixer(h, W, m, eps)
+    outs = {}
+    for on in (True, False):
+        monkeypatch.setattr(ga, "USE_TENSOR_CORES", on)
+        part = make_part("mixer", "gated_attention", attention_params(m, d, eps), W, torch.bfloat16)
+        hz = PartHarness(part, n_pages=24, page_size=16, fill=0.0)
+        outs[on] = hz.run_cut("r", h, [150, 3, 1, 1, 90, 1, 64, 2, 1])
+        check_rows(outs[on], want, "bfloat16", what=f"tensor cores {on}")
+    assert rel_rows(outs[True], outs[False]).max() < 1.5e-2
