@@ -65,7 +65,7 @@ struct TcParams {
   float* ws; int* status;
 };
 
-template <int DK, int DV>
+template <int DK, int DV, bool NARROW>
 __global__ void __launch_bounds__(TC_THREADS) sink_attention_tc_kernel(TcParams p) {
   constexpr int KS = DK + 8, VS = DV + 8;                    // elements between rows in shared memory
   extern __shared__ __align__(16) unsigned char tc_smem[];
@@ -130,15 +130,19 @@ __global__ void __launch_bounds__(TC_THREADS) sink_attention_tc_kernel(TcParams 
   cp_wait<0>();
   __syncthreads();
 
-  const bool warp_live = warp * 16 < n_rows;
+  // NARROW (a tile of up to 16 rows: decoding): the four warps share the rows and split every key tile, warp w
+  // taking its keys 16 w .. 16 w + 15; their partial results meet in shared memory at the end
+  constexpr int NB = NARROW ? 1 : TC_KT / 16;                // blocks of 16 keys a warp takes of a tile
+  const int rb = NARROW ? 0 : warp * 16;                     // the warp's first row
+  const bool warp_live = rb < n_rows;
   uint32_t qf[DK / 16][4];
   if (warp_live) {
 #pragma unroll
     for (int kk = 0; kk < DK / 16; ++kk)
-      ldsm_x4(qf[kk], Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KS + kk * 16 + (lane >> 4) * 8);
+      ldsm_x4(qf[kk], Qs + (rb + (lane & 7) + ((lane >> 3) & 1) * 8) * KS + kk * 16 + (lane >> 4) * 8);
   }
   // this thread's two rows and their positions
-  const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+  const int r_lo = rb + (lane >> 2), r_hi = r_lo + 8;
   const int pos_lo = r_lo < n_rows ? pos0 + r_lo / group : -1, pos_hi = r_hi < n_rows ? pos0 + r_hi / group : -1;
   const int first_lo = p.window > 0 ? pos_lo - p.window + 1 : 0, first_hi = p.window > 0 ? pos_hi - p.window + 1 : 0;
   float o[DV / 8][4];
@@ -146,6 +150,7 @@ __global__ void __launch_bounds__(TC_THREADS) sink_attention_tc_kernel(TcParams 
   for (int n = 0; n < DV / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
   const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
+  const int pos_last = pos0 + n_tok - 1;
 
   for (int it = 0; it < n_tiles; ++it) {
     if (it + 1 < n_tiles) {
@@ -159,30 +164,37 @@ __global__ void __launch_bounds__(TC_THREADS) sink_attention_tc_kernel(TcParams 
       const bf16* kb = Ks + (it & 1) * TC_KT * KS;
       const bf16* vb = Vs + (it & 1) * TC_KT * VS;
       const int k0 = k_begin + it * TC_KT;
-      float s[TC_KT / 8][4];
+      // every row of the tile sees every key of this key tile: nothing to mask
+      const bool all_seen = k0 + TC_KT - 1 <= min(pos0, k_end) && (p.window <= 0 || k0 > pos_last - p.window) &&
+                            n_rows - rb >= 16;
+      float s[2 * NB][4];
 #pragma unroll
-      for (int n = 0; n < TC_KT / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+      for (int n = 0; n < 2 * NB; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
 #pragma unroll
       for (int kk = 0; kk < DK / 16; ++kk) {
 #pragma unroll
-        for (int n2 = 0; n2 < TC_KT / 16; ++n2) {
+        for (int nb = 0; nb < NB; ++nb) {
+          const int n2 = NARROW ? warp : nb;
           uint32_t b[4];
           ldsm_x4(b, kb + (n2 * 16 + (lane & 7) + (lane >> 4) * 8) * KS + kk * 16 + ((lane >> 3) & 1) * 8);
-          mma16816(s[2 * n2], qf[kk], b[0], b[1]);
-          mma16816(s[2 * n2 + 1], qf[kk], b[2], b[3]);
+          mma16816(s[2 * nb], qf[kk], b[0], b[1]);
+          mma16816(s[2 * nb + 1], qf[kk], b[2], b[3]);
         }
       }
       // scale, soft cap, mask; the rows' maxima
       float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
-      for (int n = 0; n < TC_KT / 8; ++n) {
+      for (int n = 0; n < 2 * NB; ++n) {
+        const int kcol = k0 + ((NARROW ? 2 * warp : 0) + n) * 8 + (lane & 3) * 2;
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int kp = k0 + n * 8 + (lane & 3) * 2 + (e & 1);
-          const int pos = e < 2 ? pos_lo : pos_hi, first = e < 2 ? first_lo : first_hi;
           float v = s[n][e] * p.scale;
           if (p.softcap > 0.f) v = p.softcap * tc_tanh(v * inv_cap);
-          if (kp > pos || kp < first || kp > k_end) v = -INFINITY;
+          if (!all_seen) {
+            const int kp = kcol + (e & 1);
+            const int pos = e < 2 ? pos_lo : pos_hi, first = e < 2 ? first_lo : first_hi;
+            if (kp > pos || kp < first || kp > k_end) v = -INFINITY;
+          }
           s[n][e] = v;
           if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
         }
@@ -197,7 +209,7 @@ __global__ void __launch_bounds__(TC_THREADS) sink_attention_tc_kernel(TcParams 
       m_lo = mn_lo; m_hi = mn_hi;
       float sum_lo = 0.f, sum_hi = 0.f;
 #pragma unroll
-      for (int n = 0; n < TC_KT / 8; ++n) {
+      for (int n = 0; n < 2 * NB; ++n) {
         s[n][0] = __expf(s[n][0] - use_lo); s[n][1] = __expf(s[n][1] - use_lo);
         s[n][2] = __expf(s[n][2] - use_hi); s[n][3] = __expf(s[n][3] - use_hi);
         sum_lo += s[n][0] + s[n][1];
@@ -214,12 +226,13 @@ __global__ void __launch_bounds__(TC_THREADS) sink_attention_tc_kernel(TcParams 
         o[n][0] *= c_lo; o[n][1] *= c_lo; o[n][2] *= c_hi; o[n][3] *= c_hi;
       }
 #pragma unroll
-      for (int j = 0; j < TC_KT / 16; ++j) {
+      for (int nb = 0; nb < NB; ++nb) {
+        const int j = NARROW ? warp : nb;
         uint32_t ph[4], pl[4];
-        split2(s[2 * j][0], s[2 * j][1], ph[0], pl[0]);
-        split2(s[2 * j][2], s[2 * j][3], ph[1], pl[1]);
-        split2(s[2 * j + 1][0], s[2 * j + 1][1], ph[2], pl[2]);
-        split2(s[2 * j + 1][2], s[2 * j + 1][3], ph[3], pl[3]);
+        split2(s[2 * nb][0], s[2 * nb][1], ph[0], pl[0]);
+        split2(s[2 * nb][2], s[2 * nb][3], ph[1], pl[1]);
+        split2(s[2 * nb + 1][0], s[2 * nb + 1][1], ph[2], pl[2]);
+        split2(s[2 * nb + 1][2], s[2 * nb + 1][3], ph[3], pl[3]);
 #pragma unroll
         for (int n2 = 0; n2 < DV / 16; ++n2) {
           uint32_t b[4];
@@ -232,6 +245,52 @@ __global__ void __launch_bounds__(TC_THREADS) sink_attention_tc_kernel(TcParams 
       }
     }
     __syncthreads();                                         // the buffer is free for the tile after the next
+  }
+
+  if (NARROW) {
+    // the warps' partial results, [warp][row][maximum, sum, DV values], over the key buffers (all tiles are used)
+    float* part = reinterpret_cast<float*>(Ks);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int R = half ? r_hi : r_lo;
+      float* w = part + ((size_t)warp * 16 + R) * (DV + 2);
+      if ((lane & 3) == 0) { w[0] = half ? m_hi : m_lo; w[1] = half ? l_hi : l_lo; }
+#pragma unroll
+      for (int n = 0; n < DV / 8; ++n) {
+        w[2 + n * 8 + (lane & 3) * 2] = o[n][2 * half];
+        w[2 + n * 8 + (lane & 3) * 2 + 1] = o[n][2 * half + 1];
+      }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < n_rows * DV; idx += TC_THREADS) {
+      const int R = idx / DV, d = idx - R * DV;
+      const int tt = R / group, h = g * group + (R - tt * group), t = t0 + tt;
+      float m = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) m = fmaxf(m, part[((size_t)w * 16 + R) * (DV + 2)]);
+      float l = 0.f, acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {                           // in warp order
+        const float* pw = part + ((size_t)w * 16 + R) * (DV + 2);
+        if (pw[0] > -INFINITY) {
+          const float e = expf(pw[0] - m);
+          l = fmaf(e, pw[1], l);
+          acc = fmaf(e, pw[2 + d], acc);
+        }
+      }
+      if (p.splits > 1) {
+        float* w = p.ws + (((size_t)t * p.H + h) * p.splits + blockIdx.z) * (DV + 2);
+        if (d == 0) { w[0] = m; w[1] = l; }
+        w[2 + d] = acc;
+        continue;
+      }
+      const float M = p.sink ? fmaxf(m, 0.f) : m;
+      const float e = expf(m - M);
+      const float inv = 1.0f / fmaf(e, l, p.sink ? expf(0.f - M) : 0.f);
+      const float gt = p.gate ? hy_sigmoid(p.gate[(size_t)t * p.ld_gate + (size_t)h * DV + d]) : 1.f;
+      p.out[(size_t)t * p.ldo + (size_t)h * DV + d] = __float2bfloat16_rn(fmaf(e, acc, 0.f) * inv * gt);
+    }
+    return;
   }
   if (!warp_live) return;
 #pragma unroll
@@ -266,15 +325,15 @@ __global__ void __launch_bounds__(TC_THREADS) sink_attention_tc_kernel(TcParams 
   }
 }
 
-template <int DK, int DV>
+template <int DK, int DV, bool NARROW>
 int launch_tc(const TcParams& p, dim3 grid, cudaStream_t stream) {
   constexpr int smem = (TC_ROWS * (DK + 8) + 2 * TC_KT * (DK + 8) + 2 * TC_KT * (DV + 8)) * 2;
   static bool raised = false;            // once per size, before any stream capture replays the launch
   if (!raised && smem > 48 * 1024) {
-    GB_CUDA(cudaFuncSetAttribute(sink_attention_tc_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    GB_CUDA((cudaFuncSetAttribute(sink_attention_tc_kernel<DK, DV, NARROW>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)));
     raised = true;
   }
-  gb_launch(sink_attention_tc_kernel<DK, DV>, grid, dim3(TC_THREADS), smem, stream, p);
+  gb_launch(sink_attention_tc_kernel<DK, DV, NARROW>, grid, dim3(TC_THREADS), smem, stream, p);
   GB_CHECK_LAUNCH("sink_attention_tc");
   return 1;
 }
@@ -316,16 +375,19 @@ GB_OP(gb_op_sink_attention_tc) {
   p.tok_req = op_ptr<const int>(a[7]); p.tok_pos = op_ptr<const int>(a[8]); p.q_start = op_ptr<const int>(a[22]);
   p.gate = op_ptr<const float>(a[9]); p.ld_gate = a[10];
   p.out = op_ptr<bf16>(a[11]); p.ldo = a[12];
-  p.N = n; p.R = R; p.H = H; p.G = G; p.tokens_per_tile = TC_ROWS / group;
+  // every request brings one token (n == R) and its heads fill at most 16 rows: tiles of one token, whose key tiles
+  // the four warps split
+  const bool narrow = n == R && group <= 16;
+  p.N = n; p.R = R; p.H = H; p.G = G; p.tokens_per_tile = narrow ? 1 : TC_ROWS / group;
   p.scale = (float)f[0]; p.softcap = (float)f[1];
   p.window = (int)a[18]; p.sink = flags & 1;
   p.ws = op_ptr<float>(a[20]); p.status = ctx->status;
   // at most this many tiles: every request may end with a partial one
-  const int tiles = gb_div_up(n, p.tokens_per_tile) + R;
+  const int tiles = narrow ? n : gb_div_up(n, p.tokens_per_tile) + R;
   // chunks of keys when the tiles alone leave the GPU idle (decoding); whole key tiles, at fixed distances from the
   // first visible key; with a window the cut depends on the launch's sizes only
   const int span = p.window > 0 ? p.window + p.tokens_per_tile : (a[19] > 0 ? (int)a[19] : 1);
-  int wanted = 296 / (tiles * G);
+  int wanted = 592 / (tiles * G);
   if (wanted > 32) wanted = 32;
   p.splits = 1; p.chunk = span;
   if (wanted > 1 && p.ws != nullptr && !(p.window > 0 && span <= TC_KT)) {
@@ -344,7 +406,7 @@ GB_OP(gb_op_sink_attention_tc) {
   }
   const dim3 grid(tiles, G, p.splits);
   int rc;
-#define TC(DK, DV) rc = launch_tc<DK, DV>(p, grid, ctx->stream)
+#define TC(DK, DV) rc = narrow ? launch_tc<DK, DV, true>(p, grid, ctx->stream) : launch_tc<DK, DV, false>(p, grid, ctx->stream)
 #define TC_DV(DK)                                                                                    \
   do {                                                                                               \
     if (vdim == 32) TC(DK, 32); else if (vdim == 64) TC(DK, 64); else if (vdim == 96) TC(DK, 96); else TC(DK, 128); \
