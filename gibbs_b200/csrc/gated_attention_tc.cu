@@ -41,8 +41,17 @@ __device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// tanh(x) = 1 - 2 / (exp(2x) + 1) with the hardware's exponential and reciprocal: a few 2^-23 of 1
-__device__ __forceinline__ float tc_tanh(float x) { return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f); }
+// the hardware's 2^x and 1/x (a few 2^-23 relative; 2^-inf = 0, 1/inf = 0)
+__device__ __forceinline__ float tc_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float tc_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 // p as two bfloat16 terms, packed for two neighbouring columns
 __device__ __forceinline__ void split2(float x, float y, uint32_t& hi, uint32_t& lo) {
   const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
@@ -65,8 +74,11 @@ struct TcParams {
   float* ws; int* status;
 };
 
+// Scores are kept times log2(e), so that a weight is one subtraction and one 2^x: with a cap c,
+//   c tanh(s / c) log2(e) = c log2(e) - 2 c log2(e) / (2^(s * 2 log2(e) / c) + 1)      (tanh(x) = 1 - 2 / (e^(2x) + 1))
+// is a product, a 2^x, a sum, a reciprocal and a multiply-add; without one it is one product.
 template <int DK, int DV, bool NARROW>
-__global__ void __launch_bounds__(TC_THREADS) sink_attention_tc_kernel(TcParams p) {
+__global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_attention_tc_kernel(TcParams p) {
   constexpr int KS = DK + 8, VS = DV + 8;                    // elements between rows in shared memory
   extern __shared__ __align__(16) unsigned char tc_smem[];
   bf16* Qs = reinterpret_cast<bf16*>(tc_smem);               // [TC_ROWS][KS]
@@ -149,7 +161,10 @@ __global__ void __launch_bounds__(TC_THREADS) sink_attention_tc_kernel(TcParams 
 #pragma unroll
   for (int n = 0; n < DV / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
-  const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
+  constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+  const bool capped = p.softcap > 0.f;
+  const float c_in = capped ? p.scale * 2.f * LOG2E / p.softcap : p.scale * LOG2E;
+  const float c_mul = -2.f * p.softcap * LOG2E, c_add = p.softcap * LOG2E;
   const int pos_last = pos0 + n_tok - 1;
 
   for (int it = 0; it < n_tiles; ++it) {
@@ -188,8 +203,8 @@ __global__ void __launch_bounds__(TC_THREADS) sink_attention_tc_kernel(TcParams 
         const int kcol = k0 + ((NARROW ? 2 * warp : 0) + n) * 8 + (lane & 3) * 2;
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          float v = s[n][e] * p.scale;
-          if (p.softcap > 0.f) v = p.softcap * tc_tanh(v * inv_cap);
+          float v = s[n][e] * c_in;
+          if (capped) v = fmaf(c_mul, tc_rcp(tc_ex2(v) + 1.f), c_add);
           if (!all_seen) {
             const int kp = kcol + (e & 1);
             const int pos = e < 2 ? pos_lo : pos_hi, first = e < 2 ? first_lo : first_hi;
@@ -205,13 +220,13 @@ __global__ void __launch_bounds__(TC_THREADS) sink_attention_tc_kernel(TcParams 
       mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
       const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
       const float use_lo = mn_lo == -INFINITY ? 0.f : mn_lo, use_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
-      const float c_lo = __expf(m_lo - use_lo), c_hi = __expf(m_hi - use_hi);   // 0 while the row has seen nothing
+      const float c_lo = tc_ex2(m_lo - use_lo), c_hi = tc_ex2(m_hi - use_hi);   // 0 while the row has seen nothing
       m_lo = mn_lo; m_hi = mn_hi;
       float sum_lo = 0.f, sum_hi = 0.f;
 #pragma unroll
       for (int n = 0; n < 2 * NB; ++n) {
-        s[n][0] = __expf(s[n][0] - use_lo); s[n][1] = __expf(s[n][1] - use_lo);
-        s[n][2] = __expf(s[n][2] - use_hi); s[n][3] = __expf(s[n][3] - use_hi);
+        s[n][0] = tc_ex2(s[n][0] - use_lo); s[n][1] = tc_ex2(s[n][1] - use_lo);
+        s[n][2] = tc_ex2(s[n][2] - use_hi); s[n][3] = tc_ex2(s[n][3] - use_hi);
         sum_lo += s[n][0] + s[n][1];
         sum_hi += s[n][2] + s[n][3];
       }
@@ -247,6 +262,8 @@ __global__ void __launch_bounds__(TC_THREADS) sink_attention_tc_kernel(TcParams 
     __syncthreads();                                         // the buffer is free for the tile after the next
   }
 
+  m_lo *= LN2;                                               // maxima in natural units again (-inf stays)
+  m_hi *= LN2;
   if (NARROW) {
     // the warps' partial results, [warp][row][maximum, sum, DV values], over the key buffers (all tiles are used)
     float* part = reinterpret_cast<float*>(Ks);
