@@ -16,6 +16,7 @@ namespace {
 
 enum { STATUS_BAD_PAGE_READ = 2 };
 constexpr int TC_KT = 64, TC_ROWS = 64, TC_THREADS = 128;
+static_assert(TC_THREADS == 2 * TC_KT, "two threads copy a key row");
 
 __device__ __forceinline__ void cp16_zfill(void* smem, const void* gmem, bool valid) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -108,23 +109,27 @@ __global__ void __launch_bounds__(TC_THREADS, (DK + DV <= 128) ? 4 : 2) sink_att
   const int k_end = p.splits > 1 ? min(pos0 + n_tok - 1, k_begin + p.chunk - 1) : pos0 + n_tok - 1;
   const int n_tiles = k_end >= k_begin ? (k_end - k_begin) / TC_KT + 1 : 0;
 
+  // two threads a key row: the row's page is looked up once, each thread copies half of the row's 16-byte pieces
   auto load_kv = [&](int it, int buf) {
+    constexpr int PARTS = DK / 8 + DV / 8, HALF = PARTS / 2;
     const int k0 = k_begin + it * TC_KT;
     bf16* kd = Ks + buf * TC_KT * KS;
     bf16* vd = Vs + buf * TC_KT * VS;
-    for (int c = tid; c < TC_KT * (DK / 8 + DV / 8); c += TC_THREADS) {
-      const int j = c / (DK / 8 + DV / 8), part = c - j * (DK / 8 + DV / 8);
-      const int kp = k0 + j;
-      long long row = -1;
-      if (kp <= k_end) {
-        const int page = table[kp / p.page_size];
-        if (page < 0 || page >= p.n_pages) atomicExch(p.status, STATUS_BAD_PAGE_READ);
-        else row = ((long long)page * p.G + g) * p.page_size + kp % p.page_size;
-      }
-      if (part < DK / 8)
-        cp16_zfill(kd + j * KS + part * 8, p.k_pages + (row < 0 ? 0 : row) * DK + part * 8, row >= 0);
-      else
-        cp16_zfill(vd + j * VS + (part - DK / 8) * 8, p.v_pages + (row < 0 ? 0 : row) * DV + (part - DK / 8) * 8, row >= 0);
+    const int j = tid >> 1, first = (tid & 1) * HALF;
+    const int kp = k0 + j;
+    long long row = -1;
+    if (kp <= k_end) {
+      const int page = table[kp / p.page_size];
+      if (page < 0 || page >= p.n_pages) atomicExch(p.status, STATUS_BAD_PAGE_READ);
+      else row = ((long long)page * p.G + g) * p.page_size + kp % p.page_size;
+    }
+    const bf16* ksrc = p.k_pages + (row < 0 ? 0 : row) * DK;
+    const bf16* vsrc = p.v_pages + (row < 0 ? 0 : row) * DV;
+#pragma unroll
+    for (int i = 0; i < HALF; ++i) {
+      const int part = first + i;
+      if (part < DK / 8) cp16_zfill(kd + j * KS + part * 8, ksrc + part * 8, row >= 0);
+      else cp16_zfill(vd + j * VS + (part - DK / 8) * 8, vsrc + (part - DK / 8) * 8, row >= 0);
     }
     cp_commit();
   };
