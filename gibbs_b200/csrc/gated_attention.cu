@@ -105,8 +105,6 @@ __global__ void qk_prep_kernel(const float* fused, long long ld, int k_col, int 
 // chunks are empty give the same bits.
 constexpr int SA_WARPS = 8, SA_KT = 32;
 
-template <typename TC> __device__ __forceinline__ float sa_exp(float x) { return expf(x); }
-
 // The sums over chunks s of exp(m_s - M) * (l_s, acc_s) with M = max(m_s, the sink's 0): what both the
 // attention kernel (one chunk) and the merge kernel (several) divide by and multiply with.
 __device__ __forceinline__ float sa_top(float m, int sink) { return sink ? fmaxf(m, 0.f) : m; }
@@ -185,8 +183,8 @@ sink_attention_kernel(const TQ* q, long long ldq, const TC* k_pages, const TC* v
     if (k0 + lane > k_end) s = -INFINITY;
     const float m_new = fmaxf(m, warp_max(s));
     if (m_new == -INFINITY) continue;                         // (cannot happen: a tile holds a visible key)
-    const float corr = sa_exp<TC>(m - m_new);                 // 0 while m = -inf
-    const float p = sa_exp<TC>(s - m_new);                    // 0 for a key that is not seen
+    const float corr = expf(m - m_new);                 // 0 while m = -inf
+    const float p = expf(s - m_new);                    // 0 for a key that is not seen
     l = l * corr + warp_sum(p);
     m = m_new;
 #pragma unroll

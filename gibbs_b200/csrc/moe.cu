@@ -98,8 +98,8 @@ __global__ void moe_route_grouped_kernel(const float* logits, long long ld, int 
       mark[g] = b;
     }
     __syncwarp();
-    // the groups that stay closed: all but the `keep` best (a closed group's mark becomes NaN-free -inf, an
-    // open one's +inf, so that the pass below reads one flag per group)
+    // the `keep` best groups stay open: the mark of a group that is picked becomes +infinity, which no score
+    // reaches, so that the pass below reads one flag per group
     for (int k = 0; k < keep; ++k) {
       float bv = -INFINITY;
       int bg = 0x7fffffff;
